@@ -218,7 +218,7 @@ int yalm_norm_residual_rows(float *x, const float *y, int ldy, int nsum, const f
 int yalm_norm_gather_rows(float *out, const float *x, const int *rows, const float *w, int scalar_weight, float w_offset, float eps, int n_rows,
                           int dim, yalm_stream_t s);
 /* h[m, f] = act(g) * (u + up_offset), g = gu[m, f], u = gu[m, ff + f]; limit > 0: g = min(g, limit), u clamped to +-limit.
- * act: YALM_ACT_GELU, YALM_ACT_SILU, 2 = g * sigmoid(alpha g). */
+ * act: YALM_ACT_GELU, YALM_ACT_SILU, 2 = g * sigmoid(alpha g), 3 = tanh GELU with sqrt(2 / pi) to fp32 precision. */
 int yalm_glu_act_rows(float *h, const float *gu, int n, int ff, int act, float alpha, float limit, float up_offset, yalm_stream_t s);
 /* ids / wts (n, top): the experts with the largest scores (score 0: softmax, 1: sigmoid of the fp32 router logits) and
  * their scores, divided by their sum + renorm_eps if renorm.  groups > 1: experts form equal groups of neighbours, a group
@@ -308,6 +308,54 @@ int yalm_attn_sigmoid_mma(float *out, int ldo, const float *q, int ldq, const vo
 /* x[m] += a[m] (+ b[m]) + sum_{j < nsum} y[m * nsum + j]  (a, b, y optional). */
 int yalm_residual_sum_rows(float *x, const float *a, const float *b, const float *y, int ldy, int nsum, int n, int dim, yalm_stream_t s);
 int yalm_softcap_rows(float *z, int n, int dim, float cap, yalm_stream_t s);
+
+/* ---- pre-norm layers with an input convolution, latent attention, gated linear attention (csrc/ops_stack_latent.cu) ----
+ * yalm_norm_conv_rows: h = norm(x) w (layer_norm != 0: (x - mean) / sqrt(var + eps), else x / sqrt(mean x^2 + eps)); u = h + conv(h),
+ * conv(h)[m, c] = sum_j conv_w[c, j] h[m - taps + 1 + j, c]; state (taps - 1, dim): h of the positions just before the call,
+ * replaced by the call's last ones. */
+int yalm_norm_conv_rows(float *u, float *h, const float *x, const float *w, int layer_norm, float eps, const float *conv_w, float *state, int n,
+                        int dim, int taps, int pos0, const int *ctl, yalm_stream_t s);
+/* Rotary table: freq (rot_dims / 2) fp32 and a magnitude on cos and sin; interleaved != 0: pair i = channels (2 i, 2 i + 1).
+ * yalm_latent_post_rows: row m of proj (ld): [o_q, +q_rank) RMS-normed with q_norm in place; ring_buf != NULL: [o_kv, +kv_rank) RMS-normed
+ * with kv_norm and [o_kv + kv_rank, +rot_dim) with its first rot_dims channels rotated go to ring row p % ring as
+ * [kv_rank | rot_dim] (fp32 if cache_f32, else bf16). */
+int yalm_latent_post_rows(float *proj, int ld, int o_q, int q_rank, const float *q_norm, int o_kv, int kv_rank, int rot_dim, const float *kv_norm,
+                          void *ring_buf, int ring, const float *freq, float magnitude, int rot_dims, int interleaved, float eps, int cache_f32,
+                          int n, int pos0, const int *ctl, yalm_stream_t s);
+/* q (n, heads (dim + rot_dim)) -> out (n, heads (kv_rank + rot_dim)): per head [uk_h^T q_unrotated | rotated part turned by its
+ * position], uk (heads dim, kv_rank): the query against cached rows [latent | rotated key part]. */
+int yalm_latent_query_rows(float *out, int ldo, const float *q, int ldq, const void *uk, int dtype, int n, int heads, int dim, int rot_dim,
+                           int kv_rank, const float *freq, float magnitude, int rot_dims, int interleaved, int pos0, const int *ctl,
+                           yalm_stream_t s);
+/* out[m, h, :N] = w_h x[m, h, :K] (w (heads N, K)), times sigmoid(gate[m, h, :N]) if gate. */
+int yalm_head_linear_gate_rows(float *out, int ldo, const float *x, int ldx, const void *w, int dtype, const float *gate, int ldg, int n, int heads,
+                               int N, int K, yalm_stream_t s);
+/* In place: z = sigmoid(z + bias)^(1 / tau) (the decays of gated linear attention, fp32), q *= q_scale. */
+int yalm_gla_prep_rows(float *z, int ldz, const float *bias, float tau, float *q, int ldq, float q_scale, int n, int channels, yalm_stream_t s);
+/* hist slab count - 1 (slabs of `stride` floats) <- x (+ a + b + sum_j y[m nsum + j], each optional); x <- sum_j w[j] slab_j
+ * (w NULL: x <- the slab). */
+int yalm_depth_average_rows(float *x, float *hist, size_t stride, const float *w, int count, int n, int dim, const float *a, const float *b,
+                            const float *y, int ldy, int nsum, yalm_stream_t s);
+int yalm_layer_norm_gather_rows(float *out, const float *x, const int *rows, const float *w, int layer_norm, float eps, int n_rows, int dim,
+                                yalm_stream_t s);
+/* yalm_head_norm_gate_rows with silu(gate) instead of sigmoid(gate) when gate_silu != 0. */
+int yalm_head_norm_act_rows(float *out, int ldo, const float *o, int ldi, const float *gate, int ldg, const float *w, int n, int heads, int vdim,
+                            float eps, int gate_silu, yalm_stream_t s);
+/* yalm_attn_window_pool with explicit row strides of the rings (elements): values may be the first dv channels of the key rows
+ * (value_ring = key_ring, ldv = ldk). */
+int yalm_attn_window_pool_strided(float *out, int ldo, const float *q, int ldq, const void *key_ring, int ldk, const void *value_ring, int ldv,
+                                  const float *key_pool, const float *value_pool, float *workspace, int n, int n_heads, int n_kv, int dk, int dv,
+                                  int ring, int max_blocks, int window, int pool, float scale, int cache_f32, int context, int pos0,
+                                  const int *ctl, yalm_stream_t s);
+/* yalm_router_topk_rows with a stored bias per expert that only the choice sees (NULL: none) and a scale on the weights. */
+int yalm_router_bias_topk_rows(int *ids, float *wts, const float *x, int ldx, const void *wr, int dtype, int n, int n_experts, int top, int dim,
+                               int score, int renorm, float renorm_eps, int groups, int keep_groups, const float *bias, float weight_scale,
+                               yalm_stream_t s);
+/* The slot kernels with identity experts: ids >= n_real have no matrices; their slot returns the row of x (times the weight). */
+int yalm_moe_glu_slots_real(float *h, const float *x, int ldx, const void *wg, const void *wu, int dtype, const int *ids, const float *wts, int n,
+                            int top, int ff, int dim, int act, float alpha, float limit, float up_offset, int in_scale, int n_real, yalm_stream_t s);
+int yalm_moe_down_slots_real(float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int n, int top, int ff,
+                             int dim, int out_scale, int n_real, const float *x, int ldx, yalm_stream_t s);
 
 /* ---- (3a) host-pointer test entry points (src/infer.cu:890-1007 semantics) ------------------- */
 int yalm_matmul_host(float *xout, const float *x, const void *w, const float *scale, int n, int d, int dtype);

@@ -4,6 +4,7 @@
 #include "yalm_api.h"
 
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 
 namespace yalm {
@@ -151,7 +152,8 @@ int StackSpec::max_v_dim() const {
 }
 int StackSpec::max_o_dim() const {
 	int m = 0;
-	for (const LayerSpec &l : layers) m = std::max({m, l.mix.heads * l.mix.vdim, l.ssm.inner(), l.delta.heads * l.delta.vdim});
+	for (const LayerSpec &l : layers)
+		m = std::max({m, l.mix.heads * l.mix.vdim, l.ssm.inner(), l.delta.heads * l.delta.vdim, l.mix.heads * l.latent.kv_rank, l.gla.heads * l.gla.vdim});
 	return m;
 }
 int StackSpec::max_proj() const {
@@ -172,25 +174,50 @@ int StackSpec::max_aux() const {
 
 int LayerSpec::proj_width() const {
 	if (kind == MixerKind::StateSpace) return ssm.proj();
+	if (kind == MixerKind::LatentAttention) return latent.q_rank + (latent.kv_from < 0 ? latent.kv_rank + latent.rot_dim : 0) + mix.heads * mix.vdim;
+	if (kind == MixerKind::LinearAttention) return 2 * gla.heads * gla.dim + 2 * gla.heads * gla.vdim + gla.decay_rank;
 	int n = mix.heads * mix.dim + mix.kv_heads * mix.dim + (mix.values_are_keys ? 0 : mix.kv_heads * mix.vdim) + (mix.out_gate ? mix.heads * mix.vdim : 0);
 	if (kind == MixerKind::Parallel) n += 2 * delta.kv_heads * delta.dim + delta.heads * delta.vdim + delta.heads + delta.decay_rank + delta.gate_rank;
 	return n;
 }
 int LayerSpec::mixed_width() const {
 	if (kind == MixerKind::StateSpace) return ssm.inner();
+	if (kind == MixerKind::LinearAttention) return gla.heads * gla.vdim;
 	return mix.heads * mix.vdim + (kind == MixerKind::Parallel ? delta.heads * delta.vdim : 0);
 }
 int LayerSpec::conv_width() const {
 	if (kind == MixerKind::StateSpace) return ssm.conv_channels();
+	if (kind == MixerKind::LatentAttention) return mix.heads * (mix.dim + latent.rot_dim); // the queries as projected
 	return kind == MixerKind::Parallel ? 2 * delta.kv_heads * delta.dim + delta.heads * delta.vdim : 0;
 }
 int LayerSpec::aux_width() const {
+	if (kind == MixerKind::LatentAttention) return mix.heads * (latent.kv_rank + latent.rot_dim); // the queries against the cached rows
+	if (kind == MixerKind::LinearAttention) return gla.heads * gla.dim;                       // the decays
 	return kind == MixerKind::Parallel ? delta.heads * delta.dim + delta.heads * delta.vdim : 0;
 }
 int StackSpec::max_ff() const {
 	int m = 0;
-	for (const LayerSpec &l : layers) m = std::max(m, l.ffn.ff);
+	for (const LayerSpec &l : layers) m = std::max({m, l.ffn.ff, l.ffn.shared_ff});
 	return m;
+}
+
+void RotarySpec::table(std::vector<float> *freqs, float *magnitude) const {
+	const int half = dims / 2;
+	freqs->assign(half, 0.f);
+	*magnitude = 1.f;
+	std::vector<double> f(half);
+	for (int i = 0; i < half; ++i) f[i] = std::pow(base, -2.0 * i / dims);
+	if (factor > 0.0) {
+		const double pi = 3.14159265358979323846;
+		auto at = [&](double turns) { return dims * std::log(original / (2.0 * pi * turns)) / (2.0 * std::log(base)); };
+		const double lo = std::max(std::floor(at(fast)), 0.0), hi = std::min(std::ceil(at(slow)), (double)(dims - 1));
+		for (int i = 0; i < half; ++i) {
+			const double r = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001)));
+			f[i] = f[i] / factor * r + f[i] * (1.0 - r);
+		}
+		*magnitude = (float)(0.1 * std::log(factor) + 1.0);
+	}
+	for (int i = 0; i < half; ++i) (*freqs)[i] = (float)f[i];
 }
 int StackSpec::max_top() const {
 	int m = 0;
@@ -475,9 +502,171 @@ int configure_fapudra(const JValue &j, Config &cfg) {
 	return 0;
 }
 
+// ---- Fegizen ---------------------------------------------------------------------------------------------------------
+// A decoder-only stack of pre-norm layers, x <- x + mixer(N(x)), x <- x + ff(N(x)), with layer norms without bias; every
+// sublayer reads its normed input plus a short causal convolution of it; what a layer hands on is a learned weighted sum of
+// the embedding output and all layer results so far.  Mixers: latent attention (low-rank queries, one cached latent per
+// position for keys and values, a shared rotated key part, YaRN-scaled interleaved rotary positions, sliding window,
+// sigmoid output gate; a layer may read another layer's cache) or gated linear attention (matrix state with per-channel
+// decay).  Feed-forward: dense with tanh-GELU, or SiLU experts with a softmax router whose choice adds a stored bias, whose
+// last outputs are identity experts, with renormalised scaled weights and an always-on shared expert.
+std::string fegizen_tensor(int layer, TensorRole role, int expert) {
+	const std::string l = "l" + std::to_string(layer) + ".", m = l + "mix.", f = l + "mlp.";
+	const std::string e = expert >= 0 ? "e" + std::to_string(expert) + "." : "";
+	switch (role) {
+	case TensorRole::Embed: return "embed";
+	case TensorRole::FinalNorm: return "final.norm";
+	case TensorRole::Head: return "head";
+	case TensorRole::Norm1: return l + "norm1";
+	case TensorRole::Norm2: return l + "norm2";
+	case TensorRole::InConv1: return l + "canon1";
+	case TensorRole::InConv2: return l + "canon2";
+	case TensorRole::DepthWeights: return l + "dwa";
+	case TensorRole::LatentDq: return m + "dq";
+	case TensorRole::LatentDqNorm: return m + "dq.norm";
+	case TensorRole::LatentUq: return m + "uq";
+	case TensorRole::LatentDkv: return m + "dkv";
+	case TensorRole::LatentDkvNorm: return m + "dkv.norm";
+	case TensorRole::LatentUk: return m + "uk";
+	case TensorRole::LatentUv: return m + "uv";
+	case TensorRole::OutGate: return m + "g";
+	case TensorRole::Wo: return m + "o";
+	case TensorRole::Wq: return m + "q";
+	case TensorRole::Wk: return m + "k";
+	case TensorRole::Wv: return m + "v";
+	case TensorRole::GlaNorm: return m + "norm";
+	case TensorRole::GlaDecay1: return m + "a1";
+	case TensorRole::GlaDecay2: return m + "a2";
+	case TensorRole::GlaDecayBias: return m + "a2.b";
+	case TensorRole::Gate: return f + e + "gate";
+	case TensorRole::Up: return f + e + "up";
+	case TensorRole::Down: return f + e + "down";
+	case TensorRole::Router: return f + "router";
+	case TensorRole::RouterBias: return f + "correction";
+	case TensorRole::SharedGate: return f + "shared.gate";
+	case TensorRole::SharedUp: return f + "shared.up";
+	case TensorRole::SharedDown: return f + "shared.down";
+	default: break;
+	}
+	return "";
+}
+
+int fail_fegizen(const char *what) {
+	fprintf(stderr, "yalm_b200: Fegizen config.json: %s\n", what);
+	return YALM_EFORMAT;
+}
+
+int configure_fegizen(const JValue &j, Config &cfg) {
+	auto spec = std::make_shared<StackSpec>();
+	StackSpec &s = *spec;
+	s.arch = "Fegizen";
+	s.width = j["width"].integer(0);
+	s.vocab = j["vocab"].integer(0);
+	// no position table bounds the context: rotary positions, windows and recurrent state
+	s.max_positions = j["max_positions"].integer(1 << 20);
+	s.norm_eps = (float)j["norm"]["eps"].number(1e-5);
+	s.embed_scale = (float)j["embedding"]["scale"].number(1.0);
+	s.logit_scale = (float)j["logit_scale"].number(1.0);
+	s.layer_norm = true;
+	s.input_conv = j["canon"]["taps"].integer(0);
+	s.depth_average = true;
+	s.tensor_name = fegizen_tensor;
+	if (s.width < 1 || s.vocab < 1 || s.max_positions < 1) return fail_fegizen("width and vocab must be positive");
+	if (s.input_conv < 1) return fail_fegizen("canon.taps must be positive");
+	const JValue &layers = j["layers"];
+	if (!layers.is_array() || layers.arr.empty()) return fail_fegizen("'layers' must be a non-empty list");
+	for (const JValue &jl : layers.arr) {
+		LayerSpec L;
+		const std::string type = jl["type"].string_or("");
+		const JValue &m = jl["mixer"];
+		const int li = (int)s.layers.size();
+		if (type == "latent_attention") {
+			L.kind = MixerKind::LatentAttention;
+			MixerSpec &x = L.mix;
+			LatentSpec &y = L.latent;
+			x.heads = m["heads"].integer(0), x.kv_heads = 1; // every head reads the one cached row of a position
+			x.dim = m["dim"].integer(0), x.vdim = m["vdim"].integer(0);
+			x.scale = (float)m["scale"].number(1.0);
+			x.window = m["mask"]["size"].integer(0);
+			x.out_gate = true;
+			y.q_rank = m["q_rank"].integer(0), y.kv_rank = m["kv_rank"].integer(0), y.rot_dim = m["rot_dim"].integer(0);
+			y.kv_from = m["kv_from"].kind == JValue::Number ? m["kv_from"].integer(-1) : -1;
+			const JValue &r = m["rot"];
+			y.rot.dims = r["dims"].integer(y.rot_dim), y.rot.base = r["base"].number(10000.0), y.rot.interleaved = true;
+			const JValue &sc = r["scaling"];
+			if (sc.is_object()) {
+				y.rot.factor = sc["factor"].number(0.0), y.rot.original = sc["original"].number(0.0);
+				y.rot.fast = sc["fast"].number(0.0), y.rot.slow = sc["slow"].number(0.0);
+				if (!(y.rot.factor > 0.0) || !(y.rot.original > 0.0) || !(y.rot.fast > 0.0) || !(y.rot.slow > 0.0)) return fail_fegizen("bad rotary scaling");
+			}
+			if (x.heads < 1 || x.dim < 0 || x.vdim < 1 || x.window < 0 || y.q_rank < 1 || y.kv_rank < 1 || y.rot_dim < 0 || x.dim + y.rot_dim < 1)
+				return fail_fegizen("bad latent-attention sizes");
+			if (y.rot.dims < 0 || y.rot.dims % 2 || y.rot.dims > y.rot_dim || !(y.rot.base > 0.0)) return fail_fegizen("rot.dims must be even and at most rot_dim");
+			if (y.kv_from >= 0) {
+				if (y.kv_from >= li) return fail_fegizen("kv_from must name an earlier layer");
+				const LayerSpec &o = s.layers[y.kv_from];
+				if (o.kind != MixerKind::LatentAttention || o.latent.kv_from >= 0 || o.latent.kv_rank != y.kv_rank || o.latent.rot_dim != y.rot_dim)
+					return fail_fegizen("kv_from must name a latent-attention layer with its own cache and the same kv_rank and rot_dim");
+			}
+		} else if (type == "gla" || type == "gla_2") {
+			L.kind = MixerKind::LinearAttention;
+			GlaSpec &g = L.gla;
+			g.heads = m["heads"].integer(0), g.dim = m["dim"].integer(0), g.vdim = m["vdim"].integer(0);
+			g.tau = (float)m["tau"].number(1.0);
+			if (g.heads < 1 || g.dim < 1 || g.vdim < 1 || !(g.tau > 0.f)) return fail_fegizen("bad linear-attention sizes");
+		} else
+			return fail_fegizen("unknown layer type (this build has: latent_attention, gla, gla_2)");
+		const JValue &f = jl["mlp"];
+		if (f.is_object()) {
+			FfnSpec &F = L.ffn;
+			const std::string kind = f["kind"].string_or("");
+			if (kind == "dense") {
+				F.kind = FfnSpec::Dense;
+				F.ff = f["ff"].integer(0);
+				F.act = GluAct::GeluTanh;
+			} else if (kind == "moe") {
+				F.kind = FfnSpec::Moe;
+				F.ff = f["expert"]["ff"].integer(0);
+				F.act = GluAct::Silu;
+				F.experts = f["router"]["experts"].integer(0), F.top = f["router"]["top"].integer(0);
+				F.identity = f["router"]["identity"].integer(0);
+				F.router_scale = (float)f["router"]["scale"].number(1.0);
+				F.score = RouterScore::Softmax;
+				F.renormalize = true, F.renorm_eps = 1e-20f;
+				F.choice_bias = true;
+				if (f["shared"].is_object()) F.shared_ff = f["shared"]["ff"].integer(0), F.shared_act = GluAct::Silu;
+				if (F.experts < 0 || F.identity < 0 || F.top < 1 || F.top > F.experts + F.identity || F.shared_ff < 0 || (F.experts > 0 && F.ff < 1))
+					return fail_fegizen("bad router sizes");
+			} else
+				return fail_fegizen("unknown mlp kind (this build has: dense, moe)");
+			if (F.kind == FfnSpec::Dense && F.ff < 1) return fail_fegizen("bad feed-forward size");
+		}
+		s.layers.push_back(L);
+	}
+	cfg.stack = spec;
+	cfg.dim = s.width;
+	cfg.vocab_size = s.vocab;
+	cfg.n_layers = (int)s.layers.size();
+	cfg.max_seq_len = s.max_positions;
+	cfg.norm_eps = s.norm_eps;
+	cfg.hidden_dim = std::max(1, s.max_ff());
+	cfg.n_heads = cfg.n_kv_heads = 1;
+	for (const LayerSpec &l : s.layers)
+		if (l.kind == MixerKind::LatentAttention) {
+			cfg.n_heads = l.mix.heads;
+			break;
+		}
+	cfg.head_dim = 8;
+	while (cfg.n_heads * cfg.head_dim < std::max(s.max_aux(), s.max_o_dim())) cfg.head_dim *= 2;
+	cfg.rotary_dim = 0;
+	cfg.n_experts = s.max_experts(), cfg.n_experts_active = s.max_top();
+	return 0;
+}
+
 const ArchEntry kArchs[] = {
     {"Retezen", configure_retezen},
     {"Fapudra", configure_fapudra},
+    {"Fegizen", configure_fegizen},
 };
 
 } // namespace

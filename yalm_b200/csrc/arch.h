@@ -18,14 +18,16 @@ namespace yalm {
 // Normalisation of q and k before the scores.
 enum class QkNorm { None, WholeProjection /* RMS over all heads' channels at once, one weight per channel */ };
 // Gated feed-forward activations: y = act(g) * (u + up_offset), with optional clamps on g (from above) and u (both sides).
-enum class GluAct { Silu, Gelu, SigmoidScaled /* g * sigmoid(alpha * g) */ };
+enum class GluAct { Silu, Gelu /* tanh form, the reference's rounded constant */, SigmoidScaled /* g * sigmoid(alpha * g) */, GeluTanh /* tanh form, sqrt(2 / pi) to fp32 precision */ };
 // How router logits become expert scores.
 enum class RouterScore { Softmax, Sigmoid };
 // What a layer's token mixer is.
 enum class MixerKind {
 	Attention,  // MixerSpec alone
 	StateSpace, // SsmSpec: a selective state-space recurrence with a scalar decay per head
-	Parallel    // two mixers side by side on the same input, added with fixed scales: attention (MixerSpec) + gated delta rule (DeltaSpec)
+	Parallel,   // two mixers side by side on the same input, added with fixed scales: attention (MixerSpec) + gated delta rule (DeltaSpec)
+	LatentAttention, // MixerSpec + LatentSpec: queries, keys and values through low-rank latents; the cache holds the key / value latent
+	LinearAttention  // GlaSpec: a (dim, vdim) matrix state per head with one decay per key channel
 };
 // How attention scores become weights.
 enum class AttnWeights { Softmax, Sigmoid /* sigmoid(score + head bias), not normalised over the keys */ };
@@ -45,6 +47,40 @@ struct MixerSpec {
 	bool out_gate = false;       // heads * sigmoid(Wg input) before the output projection
 	int rel_rows = 0;            // > 0: a learned bias per (distance bucket, head) is added to the scaled score: distances below
 	int rel_far = 0;             // rel_rows / 2 have a row each, the rest are spaced logarithmically up to rel_far, then the last row
+};
+
+// Rotary positions: pair i of the first `dims` channels of a vector at position p turns by the angle p * f_i,
+// f_i = base^(-2 i / dims).  interleaved: pair i = channels (2 i, 2 i + 1); else (i, i + dims / 2).  factor > 0 rescales the
+// frequencies by wavelength (YaRN): with d(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(d(fast)), 0),
+// hi = min(ceil(d(slow)), dims - 1), r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1): f_i <- f_i / factor * r_i + f_i (1 - r_i),
+// and cos and sin are multiplied by 0.1 ln(factor) + 1.
+struct RotarySpec {
+	int dims = 0;
+	double base = 10000.0;
+	bool interleaved = true;
+	double factor = 0.0, original = 0.0, fast = 0.0, slow = 0.0;
+	// the table the kernels read: dims / 2 frequencies, and the factor on cos and sin (computed in double precision)
+	void table(std::vector<float> *freqs, float *magnitude) const;
+};
+
+// Latent attention: c_q = rms(W_dq x) w_q, q = W_uq c_q, per head [dim unrotated | rot_dim rotated]; W_dkv x = [kv_rank | rot_dim]:
+// the first part RMS-normed is the latent c, the rest, rotated, is one key part shared by all heads.  Per head the unrotated
+// key is W_uk c and the value W_uv c; score = (q_u . k_u + q_r . k_r) * scale.  The cache holds one row [c | k_r] per position,
+// and the products with W_uk and W_uv move to the query side: score = (W_uk^T q_u) . c + q_r . k_r, out = W_uv (sum_j p_j c_j).
+// kv_from >= 0: the layer has no W_dkv and reads that layer's cache rows with its own W_uk, W_uv, queries and window.
+// heads, dim, vdim, scale, window and the output gate are MixerSpec's.
+struct LatentSpec {
+	int q_rank = 0, kv_rank = 0, rot_dim = 0, kv_from = -1;
+	RotarySpec rot;
+};
+
+// Gated linear attention: per head a (dim, vdim) state S, S <- diag(a) S + k v^T, out = S^T q with q scaled by dim^(-1/2);
+// a = sigmoid(W_a2 W_a1 x + b)^(1 / tau) per head and key channel; per head out is RMS-normed (one weight of size vdim),
+// times silu(W_g x), then the output projection.
+struct GlaSpec {
+	int heads = 0, dim = 0, vdim = 0;
+	float tau = 1.f;
+	int decay_rank = 0; // filled from the tensors' shapes at load
 };
 
 // Selective state-space mixer (state-space duality form): one projection [z | x | B | C | dt], a short causal convolution +
@@ -80,6 +116,11 @@ struct FfnSpec {
 	int groups = 1, keep_groups = 1; // experts form `groups` equal groups of neighbours; a group scores its best expert and only
 	                             // the keep_groups best groups' experts can be chosen
 	bool weight_on_input = false; // expert(w * h) instead of w * expert(h)
+	int identity = 0;            // the router has experts + identity outputs; the last `identity` stand for experts that return their input
+	bool choice_bias = false;    // experts are chosen by score + a stored bias per router output; the weights use the score alone
+	float router_scale = 1.f;    // on the (renormalised) weights
+	int shared_ff = 0;           // > 0: one more gated feed-forward of this hidden size reads every row and is added
+	GluAct shared_act = GluAct::Silu;
 };
 
 struct LayerSpec {
@@ -87,6 +128,8 @@ struct LayerSpec {
 	MixerSpec mix;
 	SsmSpec ssm;
 	DeltaSpec delta;
+	LatentSpec latent;
+	GlaSpec gla;
 	float left_scale = 1.f, right_scale = 1.f; // Parallel: left_scale * attention + right_scale * delta rule
 	FfnSpec ffn;
 	// widths of what the layer computes per row, for scratch sizing
@@ -101,7 +144,10 @@ enum class TensorRole {
 	EmbedNorm, Shift, QBias, KBias, RelBias, HeadBias, OutGate,
 	SsmIn, SsmConv, SsmConvBias, SsmDtBias, SsmALog, SsmD, SsmNorm, SsmOut,
 	DeltaQ, DeltaK, DeltaV, DeltaQConv, DeltaKConv, DeltaVConv, DeltaBeta, DeltaALog, DeltaNorm, DeltaDecay1, DeltaDecay2, DeltaDtBias,
-	DeltaGate1, DeltaGate2, DeltaOut
+	DeltaGate1, DeltaGate2, DeltaOut,
+	InConv1, InConv2, DepthWeights, RouterBias, SharedGate, SharedUp, SharedDown,
+	LatentDq, LatentDqNorm, LatentUq, LatentDkv, LatentDkvNorm, LatentUk, LatentUv,
+	GlaNorm, GlaDecay1, GlaDecay2, GlaDecayBias
 };
 
 struct StackSpec {
@@ -119,6 +165,10 @@ struct StackSpec {
 	bool parallel_block = false;   // one norm per layer, mixer and feed-forward both read its output: x += mixer(h) + ff(h)
 	bool token_shift = false;      // the mixer reads h + (previous token's h - h) * shift; the previous h is sequence state
 	float logit_softcap = 0.f;     // > 0: logits <- cap * tanh(logits / cap)
+	bool layer_norm = false;       // norms subtract the mean: (x - mean) / sqrt(variance + eps) * w, no bias
+	int input_conv = 0;            // > 0: every sublayer reads h + conv(h), a causal convolution over time of this many taps on each
+	                               // channel of its normed input; the last taps - 1 normed inputs of both sublayers are sequence state
+	bool depth_average = false;    // what a layer hands on is a learned weighted sum of the embedding output and all layer results so far
 	// name of a tensor in the checkpoint; `expert` < 0 for tensors that are not per expert
 	std::string (*tensor_name)(int layer, TensorRole role, int expert) = nullptr;
 

@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
                                                                            const float *__restrict__ kp, const float *__restrict__ vp,
                                                                            float *__restrict__ part, int n_heads, int n_kv, int dk, int dv, int ring,
                                                                            int max_blocks, int window, int pool, float scale, int pos0,
-                                                                           const int *__restrict__ ctl) {
+                                                                           const int *__restrict__ ctl, int ldk, int ldv) {
 	extern __shared__ __align__(16) float sm[];
 	const int dkp = (dk + 7) & ~7;
 	float *qs = sm;                                    // R x dkp
@@ -312,9 +312,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
 		qs[e] = (r < nh && d < dk) ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
 	}
 	__syncthreads();
-	const CT *kbase = kc + (size_t)g * ring * dk, *vbase = vc + (size_t)g * ring * dv;
+	const CT *kbase = kc + (size_t)g * ring * ldk, *vbase = vc + (size_t)g * ring * ldv; // ldk, ldv: row strides of the rings (dk, dv when packed)
 	const float *kpb = kp ? kp + (size_t)g * max_blocks * dk : nullptr, *vpb = vp ? vp + (size_t)g * max_blocks * dv : nullptr;
-	const bool kvec_c = (dk * sizeof(CT)) % 16 == 0 && aligned16(kbase), kvec_p = (dk * 4) % 16 == 0 && aligned16(kpb);
+	const bool kvec_c = (dk * sizeof(CT)) % 16 == 0 && (ldk * sizeof(CT)) % 16 == 0 && aligned16(kbase), kvec_p = (dk * 4) % 16 == 0 && aligned16(kpb);
 	float mx[R], l[R], acc[R][DVC];
 #pragma unroll
 	for (int r = 0; r < R; ++r) {
@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
 		for (int r = 0; r < R; ++r) s[r] = 0.f;
 		if (lane < cnt) {
 			if (pooled) key_dots_f32<R>(kpb + (size_t)(idx0 + lane) * dk, qs, dkp, dk, kvec_p, s);
-			else key_dots_any<R>(kbase + (size_t)((lo + idx0 + lane) % ring) * dk, qs, dkp, dk, kvec_c, s);
+			else key_dots_any<R>(kbase + (size_t)((lo + idx0 + lane) % ring) * ldk, qs, dkp, dk, kvec_c, s);
 		}
 #pragma unroll
 		for (int r = 0; r < R; ++r) {
@@ -358,7 +358,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
 #pragma unroll
 					for (int c = 0; c < DVC; ++c) vv[j][c] = c * 32 + lane < dv ? vr[c * 32 + lane] : 0.f;
 				} else {
-					const CT *vr = vbase + (size_t)((lo + idx0 + kk) % ring) * dv;
+					const CT *vr = vbase + (size_t)((lo + idx0 + kk) % ring) * ldv;
 #pragma unroll
 					for (int c = 0; c < DVC; ++c) vv[j][c] = c * 32 + lane < dv ? cache_get(vr, c * 32 + lane) : 0.f;
 				}
@@ -637,7 +637,8 @@ __global__ void glu_act_rows_kernel(float *__restrict__ h, const float *__restri
 template <int DT>
 __global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ x, int ldx,
                                                                const void *__restrict__ wr, int E, int top, int dim, int score, int renorm,
-                                                               float renorm_eps, int groups, int keep, bool vec) {
+                                                               float renorm_eps, int groups, int keep, bool vec, const float *__restrict__ bias,
+                                                               float wscale) {
 	extern __shared__ float sc[]; // E, then E logits as they were
 	const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const float *xr = x + (size_t)m * ldx;
@@ -671,6 +672,24 @@ __global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__
 			}
 		}
 		float tot = 0.f;
+		if (bias) {
+			// the choice adds a stored bias to the score, so it cannot be ranked by the logits: rank score + bias, weigh by the score
+			float *ch = sc + E + groups; // E
+			for (int e = 0; e < E; ++e) {
+				sc[e] = sc[e] == -INFINITY ? 0.f : (score == 1 ? 1.0f / (1.0f + expf(-sc[e])) : expf(sc[e] - mx) / sum);
+				ch[e] = sc[e] + bias[e];
+			}
+			for (int j = 0; j < top; ++j) {
+				int best = -1;
+				float bz = -INFINITY;
+				for (int e = 0; e < E; ++e)
+					if (ch[e] > bz) bz = ch[e], best = e;
+				if (best < 0) best = 0;
+				ids[(size_t)m * top + j] = best, wts[(size_t)m * top + j] = sc[best];
+				tot += sc[best];
+				ch[best] = -INFINITY;
+			}
+		} else
 		for (int j = 0; j < top; ++j) {
 			int best = -1;
 			float bz = -INFINITY;
@@ -684,6 +703,8 @@ __global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__
 		}
 		if (renorm)
 			for (int j = 0; j < top; ++j) wts[(size_t)m * top + j] /= tot + renorm_eps;
+		if (wscale != 1.f)
+			for (int j = 0; j < top; ++j) wts[(size_t)m * top + j] *= wscale;
 	}
 }
 
@@ -695,10 +716,11 @@ template <int DT>
 __global__ void __launch_bounds__(128) moe_glu_slots_kernel(float *__restrict__ h, const float *__restrict__ x, int ldx, const void *__restrict__ wg,
                                                             const void *__restrict__ wu, const int *__restrict__ ids, const float *__restrict__ wts,
                                                             int top, int ff, int dim, int act, float alpha, float limit, float up_offset, int in_scale,
-                                                            bool vec) {
+                                                            bool vec, int n_real) {
 	const int s = blockIdx.y, f = blockIdx.x * 4 + (threadIdx.x >> 5);
 	if (f >= ff) return;
 	const int e = ids[s];
+	if (e >= n_real) return; // an identity expert: no matrices
 	const float *xr = x + (size_t)(s / top) * ldx;
 	const size_t off = ((size_t)e * ff + f) * dim;
 	float a = warp_dot<DT>(wg, off, xr, dim, vec), b = warp_dot<DT>(wu, off, xr, dim, vec);
@@ -708,10 +730,14 @@ __global__ void __launch_bounds__(128) moe_glu_slots_kernel(float *__restrict__ 
 template <int DT>
 __global__ void __launch_bounds__(128) moe_down_slots_kernel(float *__restrict__ y, int ldy, const float *__restrict__ h, const void *__restrict__ wd,
                                                              const int *__restrict__ ids, const float *__restrict__ wts, int ff, int dim, int out_scale,
-                                                             bool vec) {
+                                                             bool vec, int n_real, const float *__restrict__ xin, int ldx, int top) {
 	const int s = blockIdx.y, n = blockIdx.x * 4 + (threadIdx.x >> 5);
 	if (n >= dim) return;
 	const int e = ids[s];
+	if (e >= n_real) { // an identity expert returns its input
+		if ((threadIdx.x & 31) == 0) y[(size_t)s * ldy + n] = xin[(size_t)(s / top) * ldx + n] * (out_scale ? wts[s] : 1.f);
+		return;
+	}
 	float v = warp_dot<DT>(wd, ((size_t)e * dim + n) * ff, h + (size_t)s * ff, ff, vec);
 	if (out_scale) v *= wts[s];
 	if ((threadIdx.x & 31) == 0) y[(size_t)s * ldy + n] = v;
@@ -842,13 +868,14 @@ static int launch_attn_lanes(float *out, int ldo, const float *q, int ldq, const
 template <typename CT, int R, int DVC>
 static int launch_attn_wp(float *out, int ldo, const float *q, int ldq, const void *kr, const void *vr, const float *kp, const float *vp, float *ws,
                           int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool, float scale, int nsplit,
-                          int pos0, const int *ctl, cudaStream_t st) {
+                          int pos0, const int *ctl, int ldk, int ldv, cudaStream_t st) {
 	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
 	const size_t smem = sizeof(float) * ((size_t)R * ((dk + 7) & ~7) + (size_t)kAttnWarps * R * dv + kAttnWarps * R * 2);
-	if (smem > 48 * 1024) return YALM_EINVAL;
+	if (smem > 160 * 1024) return YALM_EINVAL;
+	if (smem > 48 * 1024) YALM_TRY(cudaFuncSetAttribute(attn_window_pool_kernel<CT, R, DVC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	attn_window_pool_kernel<CT, R, DVC><<<dim3(n_kv * hg, n, nsplit), kAttnWarps * 32, smem, st>>>(
 	    out, ldo, q, ldq, (const CT *)kr, (const CT *)vr, kp, vp, nsplit > 1 ? ws : nullptr, n_heads, n_kv, dk, dv, ring, max_blocks, window, pool, scale,
-	    pos0, ctl);
+	    pos0, ctl, ldk, ldv);
 	if (nsplit > 1) attn_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit);
 	return (int)cudaGetLastError();
 }
@@ -858,7 +885,18 @@ static int launch_attn_wp(float *out, int ldo, const float *q, int ldq, const vo
 extern "C" int yalm_attn_window_pool(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring, const float *key_pool,
                                      const float *value_pool, float *workspace, int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks,
                                      int window, int pool, float scale, int cache_f32, int context, int pos0, const int *ctl, yalm_stream_t s) {
-	if (!out || !q || !key_ring || !value_ring || n < 1 || n_kv < 1 || n_heads % n_kv || dv > 256 || (pool > 0 && (!key_pool || !value_pool)))
+	return yalm_attn_window_pool_strided(out, ldo, q, ldq, key_ring, dk, value_ring, dv, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring,
+	                                     max_blocks, window, pool, scale, cache_f32, context, pos0, ctl, s);
+}
+
+// The same with explicit row strides of the rings (in elements): values may live inside the key rows (value_ring = key_ring,
+// ldv = ldk, the first dv channels of a row), as a cache of shared key / value latents has them.
+extern "C" int yalm_attn_window_pool_strided(float *out, int ldo, const float *q, int ldq, const void *key_ring, int ldk, const void *value_ring, int ldv,
+                                             const float *key_pool, const float *value_pool, float *workspace, int n, int n_heads, int n_kv, int dk, int dv,
+                                             int ring, int max_blocks, int window, int pool, float scale, int cache_f32, int context, int pos0,
+                                             const int *ctl, yalm_stream_t s) {
+	if (!out || !q || !key_ring || !value_ring || n < 1 || n_kv < 1 || n_heads % n_kv || dv > 512 || ldk < dk || ldv < dv ||
+	    (pool > 0 && (!key_pool || !value_pool)))
 		return YALM_EINVAL;
 	cudaStream_t st = (cudaStream_t)s;
 	const int rep = n_heads / n_kv, R = rep >= 2 ? 4 : 1, hg = (rep + R - 1) / R;
@@ -870,7 +908,7 @@ extern "C" int yalm_attn_window_pool(float *out, int ldo, const float *q, int ld
 		const int tiles = (most_keys + 31) / 32 + 1;
 		nsplit = std::min({(296 + ctas - 1) / ctas, std::max(1, (tiles + kAttnWarps - 1) / kAttnWarps), std::max(1, kAttnMaxParts / (n * n_heads)), 64});
 	}
-	if (!cache_f32 && lanes_size(dk) && lanes_size(dv) && aligned16(key_ring) && aligned16(value_ring) && aligned16(key_pool) && aligned16(value_pool) &&
+	if (!cache_f32 && ldk == dk && ldv == dv && lanes_size(dk) && lanes_size(dv) && aligned16(key_ring) && aligned16(value_ring) && aligned16(key_pool) && aligned16(value_pool) &&
 	    !attn_lanes_off()) {
 		// heads per CTA: four share every key read; with few CTAs (decoding) a warp's instruction chain, not the reads, sets the
 		// time, so fewer heads per CTA spread the same work over more SMs (the keys then come from the L2 more than once)
@@ -886,11 +924,12 @@ extern "C" int yalm_attn_window_pool(float *out, int ldo, const float *q, int ld
 	}
 #define ATTN_CASE(CT, R_, DVC_)                                                                                                       \
 	return launch_attn_wp<CT, R_, DVC_>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring, max_blocks, \
-	                                    window, pool, scale, nsplit, pos0, ctl, st)
+	                                    window, pool, scale, nsplit, pos0, ctl, ldk, ldv, st)
 #define ATTN_DVC(CT, R_)                                                                                                              \
 	if (dv <= 64) ATTN_CASE(CT, R_, 2);                                                                                               \
 	else if (dv <= 128) ATTN_CASE(CT, R_, 4);                                                                                         \
-	else ATTN_CASE(CT, R_, 8)
+	else if (dv <= 256) ATTN_CASE(CT, R_, 8);                                                                                         \
+	else ATTN_CASE(CT, R_, 16)
 	if (cache_f32) {
 		if (R == 1) { ATTN_DVC(float, 1); }
 		else { ATTN_DVC(float, 4); }
@@ -926,29 +965,48 @@ extern "C" int yalm_glu_act_rows(float *h, const float *gu, int n, int ff, int a
 // score: 0 softmax, 1 sigmoid
 extern "C" int yalm_router_topk_rows(int *ids, float *wts, const float *x, int ldx, const void *wr, int dtype, int n, int n_experts, int top, int dim,
                                      int score, int renorm, float renorm_eps, int groups, int keep_groups, yalm_stream_t s) {
+	return yalm_router_bias_topk_rows(ids, wts, x, ldx, wr, dtype, n, n_experts, top, dim, score, renorm, renorm_eps, groups, keep_groups, nullptr, 1.f, s);
+}
+
+// bias (n_experts, optional): the experts are chosen by score + bias, the weights use the score alone; weight_scale multiplies
+// the (renormalised) weights.
+extern "C" int yalm_router_bias_topk_rows(int *ids, float *wts, const float *x, int ldx, const void *wr, int dtype, int n, int n_experts, int top, int dim,
+                                          int score, int renorm, float renorm_eps, int groups, int keep_groups, const float *bias, float weight_scale,
+                                          yalm_stream_t s) {
 	if (!ids || !wts || !x || !wr || n < 1 || top < 1 || top > n_experts || n_experts > 1024 || groups < 1 || n_experts % groups || keep_groups < 1 ||
 	    keep_groups > groups || top > keep_groups * (n_experts / groups))
 		return YALM_EINVAL;
 	const bool vec = row_vec(wr, dim, dtype) && aligned16(x) && ldx % 4 == 0;
-	DISPATCH_DT(dtype, (router_topk_rows_kernel<DT><<<n, 128, sizeof(float) * (n_experts + groups), (cudaStream_t)s>>>(
-	                       ids, wts, x, ldx, wr, n_experts, top, dim, score, renorm, renorm_eps, groups, keep_groups, vec)));
+	DISPATCH_DT(dtype, (router_topk_rows_kernel<DT><<<n, 128, sizeof(float) * (2 * n_experts + groups), (cudaStream_t)s>>>(
+	                       ids, wts, x, ldx, wr, n_experts, top, dim, score, renorm, renorm_eps, groups, keep_groups, vec, bias, weight_scale)));
 	return (int)cudaGetLastError();
 }
 
 extern "C" int yalm_moe_glu_slots(float *h, const float *x, int ldx, const void *wg, const void *wu, int dtype, const int *ids, const float *wts, int n,
                                   int top, int ff, int dim, int act, float alpha, float limit, float up_offset, int in_scale, yalm_stream_t s) {
+	return yalm_moe_glu_slots_real(h, x, ldx, wg, wu, dtype, ids, wts, n, top, ff, dim, act, alpha, limit, up_offset, in_scale, 1 << 30, s);
+}
+extern "C" int yalm_moe_down_slots(float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int n, int top, int ff,
+                                   int dim, int out_scale, yalm_stream_t s) {
+	return yalm_moe_down_slots_real(y, ldy, h, wd, dtype, ids, wts, n, top, ff, dim, out_scale, 1 << 30, nullptr, 0, s);
+}
+
+// The same with identity experts: ids >= n_real have no matrices, their slot's output is the row of x itself (times the weight).
+extern "C" int yalm_moe_glu_slots_real(float *h, const float *x, int ldx, const void *wg, const void *wu, int dtype, const int *ids, const float *wts, int n,
+                                       int top, int ff, int dim, int act, float alpha, float limit, float up_offset, int in_scale, int n_real,
+                                       yalm_stream_t s) {
 	if (!h || !x || !wg || !wu || !ids || !wts || n < 1 || top < 1) return YALM_EINVAL;
 	const bool vec = row_vec(wg, dim, dtype) && row_vec(wu, dim, dtype) && aligned16(x) && ldx % 4 == 0;
 	DISPATCH_DT(dtype, (moe_glu_slots_kernel<DT><<<dim3((ff + 3) / 4, n * top), 128, 0, (cudaStream_t)s>>>(h, x, ldx, wg, wu, ids, wts, top, ff, dim, act,
-	                                                                                                     alpha, limit, up_offset, in_scale, vec)));
+	                                                                                                     alpha, limit, up_offset, in_scale, vec, n_real)));
 	return (int)cudaGetLastError();
 }
 
-extern "C" int yalm_moe_down_slots(float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int n, int top, int ff,
-                                   int dim, int out_scale, yalm_stream_t s) {
-	if (!y || !h || !wd || !ids || !wts || n < 1 || top < 1) return YALM_EINVAL;
+extern "C" int yalm_moe_down_slots_real(float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int n, int top,
+                                        int ff, int dim, int out_scale, int n_real, const float *x, int ldx, yalm_stream_t s) {
+	if (!y || !h || !wd || !ids || !wts || n < 1 || top < 1 || (n_real < (1 << 30) && !x)) return YALM_EINVAL;
 	const bool vec = row_vec(wd, ff, dtype) && aligned16(h) && ff % 4 == 0;
-	DISPATCH_DT(dtype, (moe_down_slots_kernel<DT><<<dim3((dim + 3) / 4, n * top), 128, 0, (cudaStream_t)s>>>(y, ldy, h, wd, ids, wts, ff, dim, out_scale, vec)));
+	DISPATCH_DT(dtype, (moe_down_slots_kernel<DT><<<dim3((dim + 3) / 4, n * top), 128, 0, (cudaStream_t)s>>>(y, ldy, h, wd, ids, wts, ff, dim, out_scale, vec, n_real, x, ldx, top)));
 	return (int)cudaGetLastError();
 }
 

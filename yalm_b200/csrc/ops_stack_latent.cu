@@ -1,0 +1,362 @@
+// Row ops of pre-norm layers with an input convolution, latent attention and gated linear attention (stack.cpp).  Like the other
+// row ops every kernel takes n rows = n consecutive positions of one sequence (n = 1: a decode step), fp32 activations, and
+// positions from the argument or the device control block.  A call whose first position is 0 starts a sequence: stored state
+// is taken as zero.
+//
+//   norm_conv_rows        h = norm(x) w (layer norm without bias, or RMS), u = h + conv(h): a causal convolution over time on each
+//                         channel; the last taps - 1 rows of h are sequence state
+//   latent_post_rows      the packed projection of a latent-attention layer: the query latent RMS-normed in place; the key / value
+//                         latent RMS-normed and, beside the rotated shared key part, written to the cache row of its position
+//   latent_query_rows     per head: the unrotated query part multiplied through W_uk onto the latent's coordinates, the rotated part
+//                         turned by its position: the query against cached rows [latent | rotated key part]
+//   head_linear_gate_rows per head out = W_h x_h (the attention's sum over latents through W_uv), times sigmoid(gate)
+//   gla_prep_rows         decays a = sigmoid(z + b)^(1 / tau) and the query scale of gated linear attention
+//   depth_average_rows    keeps a layer's result and forms the weighted sum of all results so far
+//   layer_norm_gather_rows  final layer norm of the rows whose logits are wanted
+#include "common.cuh"
+
+#include <cuda_bf16.h>
+
+#include "launch.h"
+#include "stack_rows.cuh"
+
+namespace yalm {
+namespace stack {
+
+// ---- norm + input convolution -------------------------------------------------------------------------------------------
+// Row `row` of the call (negative: a position before the call, read from the state; before the sequence: zero) normed into
+// dst (dim floats of shared memory).  Two passes for the layer norm: mean, then the mean of the squared deviations.
+__device__ __forceinline__ void normed_row(float *dst, const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ state, int row,
+                                           int p0, int taps, int dim, int layer_norm, float eps, float *red) {
+	if (row < 0) {
+		const bool have = p0 + row >= 0;
+		for (int e = threadIdx.x; e < dim; e += blockDim.x) dst[e] = have ? state[(size_t)(taps - 1 + row) * dim + e] : 0.f;
+		return;
+	}
+	const float *src = x + (size_t)row * dim;
+	float mean = 0.f;
+	if (layer_norm) {
+		float s = 0.f;
+		for (int e = threadIdx.x; e < dim; e += blockDim.x) s += src[e];
+		mean = block_sum(s, red) / dim;
+	}
+	float ss = 0.f;
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+		const float d = src[e] - mean;
+		ss += d * d;
+	}
+	ss = block_sum(ss, red);
+	const float r = 1.0f / sqrtf(ss / dim + eps);
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) dst[e] = (src[e] - mean) * r * w[e];
+}
+
+// One CTA per row m: the normed rows m - taps + 1 .. m are rebuilt in shared memory (rows of the call from x, earlier ones from
+// the state (taps - 1, dim), whose slot s is the normed input of position p0 - (taps - 1) + s), u = h_m + sum_j cw[:, j] h_(m-taps+1+j).
+// h_m also goes to h.  single != 0 (one-row calls): the CTA then shifts the state itself.
+__global__ void __launch_bounds__(256) norm_conv_rows_kernel(float *__restrict__ u, float *__restrict__ h, const float *__restrict__ x,
+                                                             const float *__restrict__ w, int layer_norm, float eps, const float *__restrict__ cw,
+                                                             float *state, int dim, int taps, int single, int pos0, const int *__restrict__ ctl) {
+	extern __shared__ float hs[]; // taps x dim
+	__shared__ float red[33];
+	const int m = blockIdx.x, p0 = first_pos(ctl, pos0);
+	for (int j = 0; j < taps; ++j) normed_row(hs + (size_t)j * dim, x, w, state, m - (taps - 1) + j, p0, taps, dim, layer_norm, eps, red);
+	__syncthreads();
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+		const float hm = hs[(size_t)(taps - 1) * dim + e];
+		float acc = hm;
+		for (int j = 0; j < taps; ++j) acc = fmaf(cw[(size_t)e * taps + j], hs[(size_t)j * dim + e], acc);
+		u[(size_t)m * dim + e] = acc;
+		h[(size_t)m * dim + e] = hm;
+		if (single)
+			for (int s = 0; s < taps - 1; ++s) state[(size_t)s * dim + e] = hs[(size_t)(s + 1) * dim + e];
+	}
+}
+// After a call of n > 1 rows: slot s <- the normed input of row n - (taps - 1) + s (from h, or an old slot above s).
+__global__ void norm_conv_state_kernel(float *state, const float *__restrict__ h, int n, int dim, int taps, int pos0, const int *__restrict__ ctl) {
+	const int e = blockIdx.x * blockDim.x + threadIdx.x, p0 = first_pos(ctl, pos0);
+	if (e >= dim) return;
+	for (int s = 0; s < taps - 1; ++s) {
+		const int row = n - (taps - 1) + s;
+		state[(size_t)s * dim + e] = row >= 0 ? h[(size_t)row * dim + e] : (p0 + row >= 0 ? state[(size_t)(taps - 1 + row) * dim + e] : 0.f);
+	}
+}
+
+// ---- rotary positions ---------------------------------------------------------------------------------------------------
+// Pair i of a vector at position p turns by p * freq[i]; cos and sin carry the magnitude factor.  Position, angle and the
+// rotation are fp32.  interleaved: the pair is (2 i, 2 i + 1), else (i, i + half).
+__device__ __forceinline__ void rotate_pair(float a, float b, int p, float freq, float mag, float *ra, float *rb) {
+	const float ang = (float)p * freq;
+	float sn, cs;
+	sincosf(ang, &sn, &cs);
+	sn *= mag, cs *= mag;
+	*ra = a * cs - b * sn, *rb = b * cs + a * sn;
+}
+
+// ---- latent attention: norms, rotation, cache append ----------------------------------------------------------------------
+// Row m of the packed projection P (ld): [o_q, +q_rank) the query latent: RMS norm with weight qw in place.  With a cache of
+// its own, [o_kv, +kv_rank) RMS-normed with weight kw is the key / value latent and [o_kv + kv_rank, +rot_dim) the shared key
+// part, whose first rot_dims channels are rotated; both go to the ring row (slot p % ring) as [latent | key part].
+template <typename CT>
+__global__ void __launch_bounds__(256) latent_post_rows_kernel(float *__restrict__ P, int ld, int o_q, int q_rank, const float *__restrict__ qw, int o_kv,
+                                                               int kv_rank, int rot_dim, const float *__restrict__ kw, CT *__restrict__ ring_buf, int ring,
+                                                               const float *__restrict__ freq, float mag, int rot_dims, int interleaved, float eps,
+                                                               int pos0, const int *__restrict__ ctl) {
+	__shared__ float red[33];
+	const int m = blockIdx.x, p = first_pos(ctl, pos0) + m;
+	float *row = P + (size_t)m * ld;
+	{
+		float ss = 0.f;
+		for (int e = threadIdx.x; e < q_rank; e += blockDim.x) ss += row[o_q + e] * row[o_q + e];
+		ss = block_sum(ss, red);
+		const float r = 1.0f / sqrtf(ss / q_rank + eps);
+		for (int e = threadIdx.x; e < q_rank; e += blockDim.x) row[o_q + e] = row[o_q + e] * r * qw[e];
+	}
+	if (!ring_buf) return;
+	float ss = 0.f;
+	for (int e = threadIdx.x; e < kv_rank; e += blockDim.x) ss += row[o_kv + e] * row[o_kv + e];
+	ss = block_sum(ss, red);
+	const float r = 1.0f / sqrtf(ss / kv_rank + eps);
+	CT *dst = ring_buf + (size_t)(p % ring) * (kv_rank + rot_dim);
+	for (int e = threadIdx.x; e < kv_rank; e += blockDim.x) cache_put(dst, e, row[o_kv + e] * r * kw[e]);
+	const float *kr = row + o_kv + kv_rank;
+	const int half = rot_dims / 2;
+	for (int i = threadIdx.x; i < half; i += blockDim.x) {
+		const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+		float a, b;
+		rotate_pair(kr[ia], kr[ib], p, freq[i], mag, &a, &b);
+		cache_put(dst, kv_rank + ia, a), cache_put(dst, kv_rank + ib, b);
+	}
+	for (int e = rot_dims + threadIdx.x; e < rot_dim; e += blockDim.x) cache_put(dst, kv_rank + e, kr[e]);
+}
+
+// ---- latent attention: the query against cached rows ------------------------------------------------------------------------
+// q (n, heads (dim + rot_dim)), per head [unrotated | rotated].  out (n, heads (kv_rank + rot_dim)):
+//   out[m, h, c] = sum_d q[m, h, d] uk[h dim + d, c]   (c < kv_rank; uk (heads dim, kv_rank) as stored: W_uk^T q)
+//   out[m, h, kv_rank + j] = the rotated part turned by position p0 + m
+// so that out[m, h] . [latent_j | key part_j] is the score of head h against position j.  One CTA per (head, block of RB rows);
+// a thread owns output channels c and walks d with the rows' queries in shared memory: neighbouring threads read neighbouring
+// weights.
+constexpr int kLqRows = 8;
+template <int DT>
+__global__ void __launch_bounds__(128) latent_query_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+                                                                const void *__restrict__ uk, int n, int dim, int rot_dim, int kv_rank,
+                                                                const float *__restrict__ freq, float mag, int rot_dims, int interleaved, int pos0,
+                                                                const int *__restrict__ ctl) {
+	extern __shared__ float qs[]; // kLqRows x (dim + rot_dim)
+	const int h = blockIdx.x, m0 = blockIdx.y * kLqRows, mb = min(kLqRows, n - m0), dq = dim + rot_dim, p0 = first_pos(ctl, pos0);
+	for (int e = threadIdx.x; e < kLqRows * dq; e += blockDim.x) {
+		const int i = e / dq, d = e % dq;
+		qs[e] = i < mb ? q[(size_t)(m0 + i) * ldq + (size_t)h * dq + d] : 0.f;
+	}
+	__syncthreads();
+	const size_t obase = (size_t)h * (kv_rank + rot_dim);
+	for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+		float acc[kLqRows];
+#pragma unroll
+		for (int i = 0; i < kLqRows; ++i) acc[i] = 0.f;
+		for (int d = 0; d < dim; ++d) {
+			const float wv = Elem<DT>::get(uk, ((size_t)h * dim + d) * kv_rank + c);
+#pragma unroll
+			for (int i = 0; i < kLqRows; ++i) acc[i] = fmaf(wv, qs[i * dq + d], acc[i]);
+		}
+#pragma unroll
+		for (int i = 0; i < kLqRows; ++i)
+			if (i < mb) out[(size_t)(m0 + i) * ldo + obase + c] = acc[i];
+	}
+	const int half = rot_dims / 2;
+	for (int e = threadIdx.x; e < mb * rot_dim; e += blockDim.x) {
+		const int i = e / rot_dim, j = e % rot_dim;
+		const float *qr = qs + i * dq + dim;
+		float *dst = out + (size_t)(m0 + i) * ldo + obase + kv_rank;
+		if (j >= rot_dims) dst[j] = qr[j];
+		else if (j < half) {
+			const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+			rotate_pair(qr[ia], qr[ib], p0 + m0 + i, freq[j], mag, dst + ia, dst + ib);
+		}
+	}
+}
+
+// ---- per-head linear map with a sigmoid gate ----------------------------------------------------------------------------
+// out[m, h, j] = (sum_c w[h N + j, c] x[m, h, c]) * sigmoid(gate[m, h, j]) (gate null: no gate); w (heads N, K) row-major.
+// One CTA per (head, block of RB rows); a warp owns outputs j, its lanes stride the K inputs (coalesced weight rows), the
+// rows' inputs sit in shared memory.
+constexpr int kHlRows = 8;
+template <int DT>
+__global__ void __launch_bounds__(256) head_linear_gate_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ x, int ldx,
+                                                                    const void *__restrict__ w, const float *__restrict__ gate, int ldg, int n, int N,
+                                                                    int K) {
+	extern __shared__ float xs[]; // kHlRows x K
+	const int h = blockIdx.x, m0 = blockIdx.y * kHlRows, mb = min(kHlRows, n - m0);
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	for (int e = threadIdx.x; e < kHlRows * K; e += blockDim.x) {
+		const int i = e / K, c = e % K;
+		xs[e] = i < mb ? x[(size_t)(m0 + i) * ldx + (size_t)h * K + c] : 0.f;
+	}
+	__syncthreads();
+	for (int j = warp; j < N; j += 8) {
+		float acc[kHlRows];
+#pragma unroll
+		for (int i = 0; i < kHlRows; ++i) acc[i] = 0.f;
+		const size_t roff = ((size_t)h * N + j) * K;
+		for (int c = lane; c < K; c += 32) {
+			const float wv = Elem<DT>::get(w, roff + c);
+#pragma unroll
+			for (int i = 0; i < kHlRows; ++i) acc[i] = fmaf(wv, xs[i * K + c], acc[i]);
+		}
+#pragma unroll
+		for (int i = 0; i < kHlRows; ++i) {
+			const float v = warp_sum(acc[i]);
+			if (lane == 0 && i < mb) {
+				const size_t o = (size_t)(m0 + i) * ldo + (size_t)h * N + j;
+				out[o] = gate ? v / (1.0f + expf(-gate[(size_t)(m0 + i) * ldg + (size_t)h * N + j])) : v;
+			}
+		}
+	}
+}
+
+// ---- gated linear attention: decays and query scale ---------------------------------------------------------------------------
+// z (n, channels) in place: a = sigmoid(z + b)^(1 / tau) = exp(log sigmoid(z + b) / tau), log sigmoid(y) = min(y, 0) - log1p(exp(-|y|));
+// q (n, channels, ldq) in place: q *= q_scale.  All fp32.
+__global__ void gla_prep_rows_kernel(float *__restrict__ z, int ldz, const float *__restrict__ b, float inv_tau, float *__restrict__ q, int ldq,
+                                     float q_scale, int channels) {
+	const int m = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+	if (c >= channels) return;
+	const float y = z[(size_t)m * ldz + c] + b[c];
+	z[(size_t)m * ldz + c] = expf((fminf(y, 0.f) - log1pf(expf(-fabsf(y)))) * inv_tau);
+	q[(size_t)m * ldq + c] *= q_scale;
+}
+
+// ---- weighted sum over depth ------------------------------------------------------------------------------------------------
+// hist holds one (n, dim) slab per result (slab stride `stride` floats): slab count - 1 <- x (+ a (+ b) + sum_j slots[j]: the
+// sublayer outputs not yet added); then, with weights w (count), x <- sum_j w[j] slab_j (w null: x keeps the result).
+__global__ void depth_average_rows_kernel(float *__restrict__ x, float *__restrict__ hist, size_t stride, const float *__restrict__ w, int count,
+                                          size_t total, const float *__restrict__ a, const float *__restrict__ b, const float *__restrict__ y, int ldy,
+                                          int nsum, int dim) {
+	const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= total) return;
+	float v = x[i];
+	if (a) v += a[i];
+	if (b) v += b[i];
+	if (y) {
+		const size_t m = i / dim, e = i % dim;
+		float sy = 0.f;
+		for (int j = 0; j < nsum; ++j) sy += y[(m * nsum + j) * ldy + e];
+		v += sy;
+	}
+	hist[(size_t)(count - 1) * stride + i] = v;
+	if (w) {
+		float acc = 0.f;
+		for (int j = 0; j < count - 1; ++j) acc = fmaf(w[j], hist[(size_t)j * stride + i], acc);
+		v = fmaf(w[count - 1], v, acc);
+	}
+	x[i] = v;
+}
+
+// out[r] = layer norm (or RMS norm) of x[rows[r]] times w   (rows null: r itself)
+__global__ void __launch_bounds__(256) layer_norm_gather_rows_kernel(float *__restrict__ out, const float *__restrict__ x, const int *__restrict__ rows,
+                                                                     const float *__restrict__ w, int layer_norm, float eps, int dim) {
+	__shared__ float red[33];
+	const int r = blockIdx.x, m = rows ? rows[r] : r;
+	const float *src = x + (size_t)m * dim;
+	float mean = 0.f;
+	if (layer_norm) {
+		float s = 0.f;
+		for (int e = threadIdx.x; e < dim; e += blockDim.x) s += src[e];
+		mean = block_sum(s, red) / dim;
+	}
+	float ss = 0.f;
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+		const float d = src[e] - mean;
+		ss += d * d;
+	}
+	ss = block_sum(ss, red);
+	const float sc = 1.0f / sqrtf(ss / dim + eps);
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) out[(size_t)r * dim + e] = (src[e] - mean) * sc * w[e];
+}
+
+} // namespace stack
+} // namespace yalm
+
+using namespace yalm;
+using namespace yalm::stack;
+
+#define DISPATCH_DT(dtype, CALL)                                                                                                   \
+	switch (dtype) {                                                                                                               \
+	case YALM_F32: { constexpr int DT = YALM_F32; CALL; break; }                                                                  \
+	case YALM_F16: { constexpr int DT = YALM_F16; CALL; break; }                                                                  \
+	case YALM_BF16: { constexpr int DT = YALM_BF16; CALL; break; }                                                                \
+	default: return YALM_EINVAL;                                                                                                   \
+	}
+
+extern "C" int yalm_norm_conv_rows(float *u, float *h, const float *x, const float *w, int layer_norm, float eps, const float *conv_w, float *state, int n,
+                                   int dim, int taps, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!u || !h || !x || !w || !conv_w || n < 1 || dim < 1 || taps < 1 || (taps > 1 && !state) || u == x || h == x) return YALM_EINVAL;
+	const size_t smem = sizeof(float) * (size_t)taps * dim;
+	if (smem > 160 * 1024) return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	if (smem > 48 * 1024) YALM_TRY(cudaFuncSetAttribute(norm_conv_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	norm_conv_rows_kernel<<<n, 256, smem, st>>>(u, h, x, w, layer_norm, eps, conv_w, state, dim, taps, n == 1, pos0, ctl);
+	if (n > 1 && taps > 1) norm_conv_state_kernel<<<(dim + 255) / 256, 256, 0, st>>>(state, h, n, dim, taps, pos0, ctl);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_latent_post_rows(float *proj, int ld, int o_q, int q_rank, const float *q_norm, int o_kv, int kv_rank, int rot_dim, const float *kv_norm,
+                                     void *ring_buf, int ring, const float *freq, float magnitude, int rot_dims, int interleaved, float eps, int cache_f32,
+                                     int n, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!proj || !q_norm || n < 1 || q_rank < 1 || rot_dims < 0 || rot_dims % 2 || rot_dims > rot_dim || (rot_dims > 0 && !freq) ||
+	    (ring_buf && (!kv_norm || kv_rank < 1 || ring < 1)))
+		return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	if (cache_f32)
+		latent_post_rows_kernel<float><<<n, 256, 0, st>>>(proj, ld, o_q, q_rank, q_norm, o_kv, kv_rank, rot_dim, kv_norm, (float *)ring_buf, ring, freq, magnitude,
+		                                                  rot_dims, interleaved, eps, pos0, ctl);
+	else
+		latent_post_rows_kernel<__nv_bfloat16><<<n, 256, 0, st>>>(proj, ld, o_q, q_rank, q_norm, o_kv, kv_rank, rot_dim, kv_norm, (__nv_bfloat16 *)ring_buf, ring,
+		                                                          freq, magnitude, rot_dims, interleaved, eps, pos0, ctl);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_latent_query_rows(float *out, int ldo, const float *q, int ldq, const void *uk, int dtype, int n, int heads, int dim, int rot_dim,
+                                      int kv_rank, const float *freq, float magnitude, int rot_dims, int interleaved, int pos0, const int *ctl,
+                                      yalm_stream_t s) {
+	if (!out || !q || (!uk && dim > 0) || n < 1 || heads < 1 || dim < 0 || rot_dim < 0 || kv_rank < 1 || rot_dims < 0 || rot_dims % 2 || rot_dims > rot_dim ||
+	    (rot_dims > 0 && !freq))
+		return YALM_EINVAL;
+	const size_t smem = sizeof(float) * kLqRows * (size_t)(dim + rot_dim);
+	if (smem > 48 * 1024) return YALM_EINVAL;
+	const dim3 grid(heads, (n + kLqRows - 1) / kLqRows);
+	DISPATCH_DT(dtype, (latent_query_rows_kernel<DT><<<grid, 128, smem, (cudaStream_t)s>>>(out, ldo, q, ldq, uk, n, dim, rot_dim, kv_rank, freq, magnitude,
+	                                                                                      rot_dims, interleaved, pos0, ctl)));
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_head_linear_gate_rows(float *out, int ldo, const float *x, int ldx, const void *w, int dtype, const float *gate, int ldg, int n, int heads,
+                                          int N, int K, yalm_stream_t s) {
+	if (!out || !x || !w || n < 1 || heads < 1 || N < 1 || K < 1) return YALM_EINVAL;
+	const size_t smem = sizeof(float) * kHlRows * (size_t)K;
+	if (smem > 48 * 1024) return YALM_EINVAL;
+	const dim3 grid(heads, (n + kHlRows - 1) / kHlRows);
+	DISPATCH_DT(dtype, (head_linear_gate_rows_kernel<DT><<<grid, 256, smem, (cudaStream_t)s>>>(out, ldo, x, ldx, w, gate, ldg, n, N, K)));
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_gla_prep_rows(float *z, int ldz, const float *bias, float tau, float *q, int ldq, float q_scale, int n, int channels, yalm_stream_t s) {
+	if (!z || !bias || !q || !(tau > 0.f) || n < 1 || channels < 1) return YALM_EINVAL;
+	gla_prep_rows_kernel<<<dim3((channels + 255) / 256, n), 256, 0, (cudaStream_t)s>>>(z, ldz, bias, 1.0f / tau, q, ldq, q_scale, channels);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_depth_average_rows(float *x, float *hist, size_t stride, const float *w, int count, int n, int dim, const float *a, const float *b,
+                                       const float *y, int ldy, int nsum, yalm_stream_t s) {
+	if (!x || !hist || count < 1 || n < 1 || dim < 1 || stride < (size_t)n * dim || (y && nsum < 1)) return YALM_EINVAL;
+	const size_t total = (size_t)n * dim;
+	depth_average_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)s>>>(x, hist, stride, w, count, total, a, b, y, ldy, nsum, dim);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_layer_norm_gather_rows(float *out, const float *x, const int *rows, const float *w, int layer_norm, float eps, int n_rows, int dim,
+                                           yalm_stream_t s) {
+	if (!out || !x || !w || n_rows < 1 || dim < 1) return YALM_EINVAL;
+	layer_norm_gather_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)s>>>(out, x, rows, w, layer_norm, eps, dim);
+	return (int)cudaGetLastError();
+}

@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(1024) gated_group_norm_rows_kernel(float *__re
 // out[m, h, c] = o / sqrt(mean_c o^2 + eps) * w[c] * sigmoid(gate[m, h, c]); one warp per (row, head), w shared by the heads
 __global__ void __launch_bounds__(128) head_norm_gate_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ o, int ldi,
                                                                   const float *__restrict__ gate, int ldg, const float *__restrict__ w, int H, int P,
-                                                                  float eps) {
+                                                                  float eps, int gate_silu) {
 	const int m = blockIdx.y, h = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
 	if (h >= H) return;
 	const float *row = o + (size_t)m * ldi + h * P;
@@ -328,7 +328,10 @@ __global__ void __launch_bounds__(128) head_norm_gate_rows_kernel(float *__restr
 	for (int c = lane; c < P; c += 32) ss += row[c] * row[c];
 	ss = warp_sum(ss);
 	const float r = 1.0f / sqrtf(ss / P + eps);
-	for (int c = lane; c < P; c += 32) out[(size_t)m * ldo + h * P + c] = row[c] * r * w[c] * sigmoidf_(gate[(size_t)m * ldg + h * P + c]);
+	for (int c = lane; c < P; c += 32) {
+		const float g = gate[(size_t)m * ldg + h * P + c];
+		out[(size_t)m * ldo + h * P + c] = row[c] * r * w[c] * (gate_silu ? siluf_(g) : sigmoidf_(g));
+	}
 }
 
 // ---- sigmoid attention -----------------------------------------------------------------------------------------------------
@@ -685,8 +688,14 @@ extern "C" int yalm_gated_group_norm_rows(float *out, int ldo, const float *y, i
 
 extern "C" int yalm_head_norm_gate_rows(float *out, int ldo, const float *o, int ldi, const float *gate, int ldg, const float *w, int n, int heads, int vdim,
                                         float eps, yalm_stream_t s) {
+	return yalm_head_norm_act_rows(out, ldo, o, ldi, gate, ldg, w, n, heads, vdim, eps, 0, s);
+}
+
+// gate_silu != 0: the gate is silu(gate) instead of sigmoid(gate)
+extern "C" int yalm_head_norm_act_rows(float *out, int ldo, const float *o, int ldi, const float *gate, int ldg, const float *w, int n, int heads, int vdim,
+                                       float eps, int gate_silu, yalm_stream_t s) {
 	if (!out || !o || !gate || !w || n < 1 || heads < 1 || vdim < 1) return YALM_EINVAL;
-	head_norm_gate_rows_kernel<<<dim3((heads + 3) / 4, n), 128, 0, (cudaStream_t)s>>>(out, ldo, o, ldi, gate, ldg, w, heads, vdim, eps);
+	head_norm_gate_rows_kernel<<<dim3((heads + 3) / 4, n), 128, 0, (cudaStream_t)s>>>(out, ldo, o, ldi, gate, ldg, w, heads, vdim, eps, gate_silu);
 	return (int)cudaGetLastError();
 }
 

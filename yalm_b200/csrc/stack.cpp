@@ -66,6 +66,20 @@ struct StackLayer {
 	float *conv_state = nullptr;             // (channels, taps - 1)
 	float *scan_state = nullptr;             // (heads, vdim, state | dim)
 	std::vector<std::pair<void **, size_t>> state_allocs; // device buffers beside the rings, taken from the arena
+	// ---- pre-norm layers with an input convolution and a weighted sum over depth ----
+	float *inconv1 = nullptr, *inconv2 = nullptr;             // (dim, taps) each
+	float *inconv1_state = nullptr, *inconv2_state = nullptr; // (taps - 1, dim): the sublayer's last normed inputs
+	float *depth_w = nullptr;                                 // (layer + 2)
+	// latent attention: columns [query latent | key / value latent + shared key part (own cache only) | gate]
+	int o_kv = 0, kv_owner = -1;                              // kv_owner: the layer whose ring this layer reads (itself, or kv_from)
+	void *wuq = nullptr, *wuk = nullptr, *wuv = nullptr;      // (heads (dim + rot), q_rank), (heads dim, kv_rank), (heads vdim, kv_rank)
+	float *rot_freq = nullptr;                                // rotary frequencies (rot dims / 2)
+	float rot_mag = 1.f;
+	// gated linear attention: columns [q | k | v | gate | decay stage 1]; wa2, d_dt_bias (the decay's bias), mix_norm, scan_state as above
+	int o_v = 0;
+	// experts: the choice bias; the shared expert
+	float *router_bias = nullptr;
+	void *wsgu = nullptr, *wsdown = nullptr;                  // (2 shared_ff, dim), (dim, shared_ff)
 };
 
 } // namespace yalm
@@ -106,6 +120,10 @@ int Config::from_json(YALMData &data, int context, int compute) {
 				fprintf(stderr, "yalm_b200: layer %d: the delta rule's two-stage projections are missing\n", i);
 				return YALM_EFORMAT;
 			}
+		}
+		if (l.kind == yalm::MixerKind::LinearAttention && (l.gla.decay_rank = rows(TensorRole::GlaDecay1)) < 1) {
+			fprintf(stderr, "yalm_b200: layer %d: the decay's two-stage projection is missing\n", i);
+			return YALM_EFORMAT;
 		}
 		if (l.mix.rel_rows > 0 && (l.mix.rel_rows = rows(TensorRole::RelBias)) < 2) {
 			fprintf(stderr, "yalm_b200: layer %d: the distance-bias table needs at least two rows\n", i);
@@ -213,11 +231,13 @@ struct Model::StackScratch {
 	      *logits = nullptr, *probs = nullptr;
 	void *a16 = nullptr, *a16e = nullptr, *a16r = nullptr; // 16-bit operands of the tensor-core products: main stream, experts' stream, second mixer's stream
 	float *hs = nullptr, *conv = nullptr, *aux = nullptr, *scan = nullptr, *att2 = nullptr, *y1 = nullptr, *y2 = nullptr; // parallel blocks
+	float *hist = nullptr;    // weighted sum over depth: the embedding output and every layer's result of the current rows, (layers + 1, cap, width)
 	float *attn_ws = nullptr; // split partials of decode-sized attention calls
 	int *ids = nullptr, *tokens = nullptr, *want = nullptr, *targets = nullptr;
 	float *moe_gu = nullptr, *moe_ys = nullptr; // experts on the tensor cores: (gate | up) and down outputs of the slots sorted by expert
 	int *order = nullptr;                       // slot at every place of that order
 	unsigned *ticket = nullptr; // arrival counter of the one-row products with a fused tail (zero between launches)
+	int hist_slabs = 0;
 	std::vector<Placement> placements; // filled by build_stack, consumed by cuda_stack
 	// decode rows of a parallel block: its independent sublayers (experts, the second mixer) run on side streams that fork from and
 	// join the caller's stream through these events; inside a captured step they become parallel branches of the graph
@@ -258,6 +278,7 @@ void Model::build_stack(YALMData &data) {
 	pl.push_back({&token_embedding_table, {mat(tensor(0, TensorRole::Embed, -1, {s.vocab, s.width}))}});
 	if (s.learned_positions) pl.push_back({&_pos_table, {mat(tensor(0, TensorRole::Positions, -1, {s.max_positions, s.width}))}});
 	pl.push_back({(void **)&rms_final_weight, {vec32(s.norm_scalar ? tensor(0, TensorRole::FinalNorm, -1, {}) : tensor(0, TensorRole::FinalNorm, -1, {s.width}))}});
+	if (s.depth_average) _scratch->hist_slabs = (int)s.layers.size() + 1;
 	if (s.embed_norm) pl.push_back({(void **)&_embed_norm, {vec32(s.norm_scalar ? tensor(0, TensorRole::EmbedNorm, -1, {}) : tensor(0, TensorRole::EmbedNorm, -1, {s.width}))}});
 	pl.push_back({&wcls, {mat(tensor(0, TensorRole::Head, -1, {s.vocab, s.width}))}});
 	bool have_first = false;
@@ -359,6 +380,99 @@ void Model::build_stack(YALMData &data) {
 			_stack.push_back(L);
 			continue;
 		}
+		if (L->spec.kind == yalm::MixerKind::LatentAttention || L->spec.kind == yalm::MixerKind::LinearAttention) {
+			// ---- pre-norm layer: norm + input convolution per sublayer, one packed projection of the mixer's input, weighted sum over depth ----
+			const int W = s.width, taps = s.input_conv;
+			const yalm::LayerSpec &ls = L->spec;
+			const FfnSpec &f = ls.ffn;
+			pl.push_back({(void **)&L->norm1, {vec32(tensor(i, TensorRole::Norm1, -1, {W}))}});
+			if (taps > 0) {
+				pl.push_back({(void **)&L->inconv1, {vec32(tensor(i, TensorRole::InConv1, -1, {W, taps}))}});
+				if (taps > 1) L->state_allocs.push_back({(void **)&L->inconv1_state, (size_t)(taps - 1) * W * 4});
+			}
+			if (s.depth_average) pl.push_back({(void **)&L->depth_w, {vec32(tensor(i, TensorRole::DepthWeights, -1, {i + 2}))}});
+			Placement proj{&L->wproj, {}};
+			if (ls.kind == yalm::MixerKind::LatentAttention) {
+				const yalm::LatentSpec &a = ls.latent;
+				const int no = m.heads * m.vdim, row = a.kv_rank + a.rot_dim;
+				const bool own = a.kv_from < 0;
+				L->o_q = 0, L->o_kv = a.q_rank, L->o_gate = a.q_rank + (own ? row : 0);
+				L->kv_owner = own ? i : a.kv_from;
+				proj.parts.push_back(mat(tensor(i, TensorRole::LatentDq, -1, {a.q_rank, W})));
+				if (own) proj.parts.push_back(mat(tensor(i, TensorRole::LatentDkv, -1, {row, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::OutGate, -1, {no, W})));
+				pl.push_back({(void **)&L->qnorm, {vec32(tensor(i, TensorRole::LatentDqNorm, -1, {a.q_rank}))}});
+				if (own) pl.push_back({(void **)&L->knorm, {vec32(tensor(i, TensorRole::LatentDkvNorm, -1, {a.kv_rank}))}});
+				pl.push_back({&L->wuq, {mat(tensor(i, TensorRole::LatentUq, -1, {m.heads * (m.dim + a.rot_dim), a.q_rank}))}});
+				if (m.dim > 0) pl.push_back({&L->wuk, {mat(tensor(i, TensorRole::LatentUk, -1, {m.heads * m.dim, a.kv_rank}))}});
+				pl.push_back({&L->wuv, {mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
+				pl.push_back({&L->wo, {mat(tensor(i, TensorRole::Wo, -1, {W, no}))}});
+				if (a.rot.dims > 0) {
+					std::vector<float> fr;
+					a.rot.table(&fr, &L->rot_mag);
+					_host_converted.emplace_back(fr.size() * sizeof(float));
+					memcpy(_host_converted.back().data(), fr.data(), fr.size() * sizeof(float));
+					pl.push_back({(void **)&L->rot_freq, {{_host_converted.back().data(), fr.size() * sizeof(float)}}});
+				}
+				if (own) {
+					// one cache row [latent | rotated key part] per position; the ring covers the widest window of the layers that read it
+					int span = m.window;
+					bool unbounded = m.window == 0;
+					for (int k = i + 1; k < (int)s.layers.size(); ++k)
+						if (s.layers[k].kind == yalm::MixerKind::LatentAttention && s.layers[k].latent.kv_from == i)
+							span = std::max(span, s.layers[k].mix.window), unbounded = unbounded || s.layers[k].mix.window == 0;
+					L->ring = unbounded ? c.max_seq_len : std::min(c.max_seq_len, (span + c.stack_chunk + 63) / 64 * 64);
+					const size_t cb = c.weight_dtype == DType::F32 ? 4 : 2;
+					L->state_allocs.push_back({&L->kring, (size_t)L->ring * row * cb});
+				}
+				if (a.kv_rank > 512) die("latent attention: latents above 512 channels are not built");
+			} else {
+				const yalm::GlaSpec &g = ls.gla;
+				const int hd = g.heads * g.dim, hp = g.heads * g.vdim;
+				L->o_q = 0, L->o_k = hd, L->o_v = 2 * hd, L->o_gate = 2 * hd + hp, L->o_a1 = 2 * hd + 2 * hp;
+				proj.parts.push_back(mat(tensor(i, TensorRole::Wq, -1, {hd, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::Wk, -1, {hd, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::Wv, -1, {hp, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::OutGate, -1, {hp, W})));
+				proj.parts.push_back(mat(tensor(i, TensorRole::GlaDecay1, -1, {g.decay_rank, W})));
+				pl.push_back({&L->wa2, {mat(tensor(i, TensorRole::GlaDecay2, -1, {hd, g.decay_rank}))}});
+				pl.push_back({(void **)&L->d_dt_bias, {vec32(tensor(i, TensorRole::GlaDecayBias, -1, {hd}))}});
+				pl.push_back({(void **)&L->mix_norm, {vec32(tensor(i, TensorRole::GlaNorm, -1, {g.vdim}))}});
+				pl.push_back({&L->wo, {mat(tensor(i, TensorRole::Wo, -1, {W, hp}))}});
+				L->state_allocs.push_back({(void **)&L->scan_state, (size_t)g.heads * g.vdim * g.dim * 4});
+				if (g.dim > 256) die("linear attention: key sizes above 256 are not built");
+			}
+			pl.push_back(proj);
+			if (f.kind != FfnSpec::None) {
+				pl.push_back({(void **)&L->norm2, {vec32(tensor(i, TensorRole::Norm2, -1, {W}))}});
+				if (taps > 0) {
+					pl.push_back({(void **)&L->inconv2, {vec32(tensor(i, TensorRole::InConv2, -1, {W, taps}))}});
+					if (taps > 1) L->state_allocs.push_back({(void **)&L->inconv2_state, (size_t)(taps - 1) * W * 4});
+				}
+			}
+			if (f.kind == FfnSpec::Dense) {
+				pl.push_back({&L->wgu, {mat(tensor(i, TensorRole::Gate, -1, {f.ff, W})), mat(tensor(i, TensorRole::Up, -1, {f.ff, W}))}});
+				pl.push_back({&L->wdown, {mat(tensor(i, TensorRole::Down, -1, {W, f.ff}))}});
+			} else if (f.kind == FfnSpec::Moe) {
+				if (f.experts > 0) {
+					Placement g{&L->wg, {}}, u{&L->wu, {}}, d{&L->wdown, {}};
+					for (int e = 0; e < f.experts; ++e) {
+						g.parts.push_back(mat(tensor(i, TensorRole::Gate, e, {f.ff, W})));
+						u.parts.push_back(mat(tensor(i, TensorRole::Up, e, {f.ff, W})));
+						d.parts.push_back(mat(tensor(i, TensorRole::Down, e, {W, f.ff})));
+					}
+					pl.push_back(g), pl.push_back(u), pl.push_back(d);
+				}
+				pl.push_back({&L->router, {mat(tensor(i, TensorRole::Router, -1, {f.experts + f.identity, W}))}});
+				if (f.choice_bias) pl.push_back({(void **)&L->router_bias, {vec32(tensor(i, TensorRole::RouterBias, -1, {f.experts + f.identity}))}});
+				if (f.shared_ff > 0) {
+					pl.push_back({&L->wsgu, {mat(tensor(i, TensorRole::SharedGate, -1, {f.shared_ff, W})), mat(tensor(i, TensorRole::SharedUp, -1, {f.shared_ff, W}))}});
+					pl.push_back({&L->wsdown, {mat(tensor(i, TensorRole::SharedDown, -1, {W, f.shared_ff}))}});
+				}
+			}
+			_stack.push_back(L);
+			continue;
+		}
 		const int nq = m.heads * m.dim, nk = m.kv_heads * m.dim, nv = m.kv_heads * m.vdim, no = m.heads * m.vdim, W = s.width;
 		pl.push_back({&L->wqkv,
 		              {mat(tensor(i, TensorRole::Wq, -1, {nq, W})), mat(tensor(i, TensorRole::Wk, -1, {nk, W})), mat(tensor(i, TensorRole::Wv, -1, {nv, W}))}});
@@ -404,6 +518,11 @@ void Model::build_stack(YALMData &data) {
 		}
 }
 
+// layers whose cache and state are all in state_allocs (no key / value ring pair of the generic attention)
+static bool own_state(const StackLayer &L) {
+	return L.spec.kind == yalm::MixerKind::LatentAttention || L.spec.kind == yalm::MixerKind::LinearAttention;
+}
+
 void Model::cuda_stack(int device) {
 	Config &c = *config;
 	const StackSpec &s = *c.stack;
@@ -417,7 +536,7 @@ void Model::cuda_stack(int device) {
 	for (auto &L : _stack) {
 		const yalm::MixerSpec &m = L->spec.mix;
 		for (auto &sa : L->state_allocs) need += DeviceArena::padded(sa.second);
-		if (s.parallel_block) continue;
+		if (s.parallel_block || own_state(*L)) continue;
 		need += DeviceArena::padded((size_t)m.kv_heads * L->ring * m.dim * cb) + DeviceArena::padded((size_t)m.kv_heads * L->ring * m.vdim * cb);
 		if (m.pool > 0)
 			need += DeviceArena::padded((size_t)m.kv_heads * L->max_blocks * m.dim * 4) + DeviceArena::padded((size_t)m.kv_heads * L->max_blocks * m.vdim * 4);
@@ -442,7 +561,7 @@ void Model::cuda_stack(int device) {
 			up.zero(*sa.first, sa.second);
 			_device_bytes += sa.second;
 		}
-		if (s.parallel_block) continue;
+		if (s.parallel_block || own_state(*L)) continue;
 		const size_t kb = (size_t)m.kv_heads * L->ring * m.dim * cb, vb = (size_t)m.kv_heads * L->ring * m.vdim * cb;
 		L->kring = _arena->take(kb), L->vring = _arena->take(vb);
 		if (!L->kring || !L->vring) die("device arena exhausted (cache)");
@@ -466,7 +585,11 @@ void Model::cuda_stack(int device) {
 	S.cap = c.stack_chunk;
 	const size_t cap = S.cap, W = s.width, top = std::max(1, s.max_top()), ff = std::max(1, s.max_ff());
 	const size_t nqkv = std::max((size_t)s.max_q_dim() + s.max_kv_dim() + s.max_v_dim(), (size_t)s.max_proj());
-	const size_t pb = s.parallel_block ? 1 : 0, nconv = std::max(1, s.max_conv()), naux = std::max(1, s.max_aux()), no = std::max(1, s.max_o_dim());
+	bool side_bufs = s.parallel_block; // buffers beside q | k | v: shifted / convolved inputs, second-stage products, per-mixer outputs
+	for (auto &L : _stack) side_bufs = side_bufs || own_state(*L);
+	for (auto &L : _stack) // a layer that reads another layer's cache rows
+		if (L->kv_owner >= 0 && L->kv_owner < (int)_stack.size() && !L->kring) L->kring = _stack[L->kv_owner]->kring, L->ring = _stack[L->kv_owner]->ring;
+	const size_t pb = side_bufs ? 1 : 0, nconv = std::max(1, s.max_conv()), naux = std::max(1, s.max_aux()), no = std::max(1, s.max_o_dim());
 	const size_t kmax = std::max({W, (size_t)s.max_o_dim(), ff});
 	const bool moe = s.max_experts() > 0 && c.weight_dtype != DType::F32; // the grouped route needs 16-bit operands
 	auto pad = [](size_t b) { return (b + 255) / 256 * 256; };
@@ -479,9 +602,10 @@ void Model::cuda_stack(int device) {
 	             {(void **)&S.xn, 4 * cap * W},          {(void **)&S.logits, 4 * cap * (size_t)s.vocab}, {(void **)&S.probs, 4 * cap},
 	             {(void **)&S.a16, 2 * cap * top * kmax}, {(void **)&S.a16e, pb * 2 * cap * top * kmax}, {(void **)&S.a16r, pb * 2 * cap * top * kmax}, {(void **)&S.ids, 4 * cap * top},       {(void **)&S.tokens, 4 * cap},
 	             {(void **)&S.want, 4 * cap},            {(void **)&S.targets, 4 * cap},
-	             {(void **)&S.attn_ws, 4 * yalm_attn_window_pool_workspace(256)}, {(void **)&S.ticket, 256},
+	             {(void **)&S.attn_ws, 4 * yalm_attn_window_pool_workspace(512)}, {(void **)&S.ticket, 256},
 	             {(void **)&S.hs, pb * 4 * cap * W}, {(void **)&S.conv, pb * 4 * cap * nconv}, {(void **)&S.aux, pb * 4 * cap * naux},
 	             {(void **)&S.scan, pb * 4 * cap * no}, {(void **)&S.att2, pb * 4 * cap * no}, {(void **)&S.y1, pb * 4 * cap * W}, {(void **)&S.y2, pb * 4 * cap * W},
+	             {(void **)&S.hist, 4 * cap * W * (size_t)S.hist_slabs},
 	             {(void **)&S.moe_gu, moe ? 4 * cap * top * 2 * ff : 0}, {(void **)&S.moe_ys, moe ? 4 * cap * top * W : 0}, {(void **)&S.order, 4 * cap * top}};
 	size_t total = 0;
 	for (auto &sl : slots) total += pad(sl.bytes);
@@ -557,21 +681,24 @@ static bool moe_grouped_off() { // YALM_STACK_MOE_TC=0: A/B against the slot ker
 int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const float *x, void *a16, int n, int act, cudaStream_t st) {
 	const Config &c = *config;
 	const FfnSpec &f = L.spec.ffn;
-	const int W = c.stack->width, ff = f.ff, top = f.top, E = f.experts, ns = n * top, bf16 = c.weight_dtype == DType::BF16;
-	std::vector<int> ids(ns), order(ns), start(E + 1, 0);
+	const int W = c.stack->width, ff = f.ff, top = f.top, E = f.experts, EA = f.experts + f.identity, ns = n * top, bf16 = c.weight_dtype == DType::BF16;
+	std::vector<int> ids(ns), order(ns), start(EA + 1, 0); // identity experts sort behind the real ones and take no product
 	ST_TRY(cudaMemcpyAsync(ids.data(), S.ids, sizeof(int) * ns, cudaMemcpyDeviceToHost, st));
 	ST_TRY(cudaStreamSynchronize(st));
 	for (int s = 0; s < ns; ++s) {
-		if (ids[s] < 0 || ids[s] >= E) return YALM_EINVAL;
+		if (ids[s] < 0 || ids[s] >= EA) return YALM_EINVAL;
 		++start[ids[s] + 1];
 	}
-	for (int e = 0; e < E; ++e) start[e + 1] += start[e];
+	for (int e = 0; e < EA; ++e) start[e + 1] += start[e];
+	const int nr = start[E]; // slots of real experts
 	{
 		std::vector<int> at(start.begin(), start.end() - 1);
 		for (int s = 0; s < ns; ++s) order[at[ids[s]]++] = s; // stable: slots of an expert stay in row order
 	}
 	ST_TRY(cudaMemcpyAsync(S.order, order.data(), sizeof(int) * ns, cudaMemcpyHostToDevice, st));
-	ST_TRY(yalm_moe_gather_rows16(a16, x, W, S.order, S.wts, ns, top, W, bf16, f.weight_on_input ? 1 : 0, st));
+	if (f.identity > 0) ST_TRY(yalm_moe_down_slots_real(S.y, W, S.h, L.wdown, static_cast<int>(c.weight_dtype), S.ids, S.wts, n, top, ff, W, f.weight_on_input ? 0 : 1, 0, x, W, st)); // n_real = 0: every slot as an identity slot; the real ones are overwritten below
+	if (nr == 0) return (int)cudaGetLastError();
+	ST_TRY(yalm_moe_gather_rows16(a16, x, W, S.order, S.wts, nr, top, W, bf16, f.weight_on_input ? 1 : 0, st));
 	const size_t es = dtype_size(c.weight_dtype);
 	for (int e = 0; e < E; ++e) {
 		const int m = start[e + 1] - start[e];
@@ -581,15 +708,15 @@ int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const f
 		ST_TRY(yalm_gemm_16(gu, 2 * ff, a, static_cast<const char *>(L.wg) + (size_t)e * ff * W * es, m, ff, W, 0, bf16, 1.f, st));
 		ST_TRY(yalm_gemm_16(gu + ff, 2 * ff, a, static_cast<const char *>(L.wu) + (size_t)e * ff * W * es, m, ff, W, 0, bf16, 1.f, st));
 	}
-	ST_TRY(yalm_glu_act_rows(S.h, S.moe_gu, ns, ff, act, f.act_alpha, f.limit, f.up_offset, st));
-	ST_TRY(yalm_cast_rows16(a16, S.h, ff, ns, ff, bf16, st));
+	ST_TRY(yalm_glu_act_rows(S.h, S.moe_gu, nr, ff, act, f.act_alpha, f.limit, f.up_offset, st));
+	ST_TRY(yalm_cast_rows16(a16, S.h, ff, nr, ff, bf16, st));
 	for (int e = 0; e < E; ++e) {
 		const int m = start[e + 1] - start[e];
 		if (!m) continue;
 		ST_TRY(yalm_gemm_16(S.moe_ys + (size_t)start[e] * W, W, static_cast<const char *>(a16) + (size_t)start[e] * ff * 2,
 		                    static_cast<const char *>(L.wdown) + (size_t)e * W * ff * es, m, W, ff, 0, bf16, 1.f, st));
 	}
-	ST_TRY(yalm_moe_scatter_rows(S.y, W, S.moe_ys, W, S.order, S.wts, ns, W, f.weight_on_input ? 0 : 1, st));
+	ST_TRY(yalm_moe_scatter_rows(S.y, W, S.moe_ys, W, S.order, S.wts, nr, W, f.weight_on_input ? 0 : 1, st));
 	return (int)cudaGetLastError(); // `order` was pageable host memory: the copy call returned after staging it
 }
 
@@ -707,6 +834,90 @@ int Model::stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int 
 	return yalm_residual_sum_rows(S.x, S.y1, mix_b, S.y, W, nsum, n, W, st);
 }
 
+static int glu_act_code(yalm::GluAct a) {
+	return a == yalm::GluAct::SigmoidScaled ? 2 : a == yalm::GluAct::GeluTanh ? 3 : a == yalm::GluAct::Silu ? YALM_ACT_SILU : YALM_ACT_GELU;
+}
+
+// One pre-norm layer over n rows: u = N1(x) + conv(N1(x)), x += mixer(u); v = N2(x) + conv(N2(x)), x += ff(v); then the
+// layer's result joins the earlier ones and x becomes their weighted sum.  The mixer is latent attention over cached rows
+// [latent | rotated key part] (its own, or another layer's) or gated linear attention over a matrix state.  What the rows
+// leave for the next call (normed inputs of both convolutions, cache rows, matrix state) is written by the ops themselves.
+int Model::stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int index, int n, int pos0, const int *ctl, cudaStream_t st) {
+	const Config &c = *config;
+	const StackSpec &sp = *c.stack;
+	const yalm::LayerSpec &ls = L.spec;
+	const int dt = static_cast<int>(c.weight_dtype), W = sp.width, f32 = c.weight_dtype == DType::F32, taps = std::max(1, sp.input_conv);
+	const int ldp = ls.proj_width();
+	float *P = S.qkv;
+	// ---- token mixer ----
+	ST_TRY(yalm_norm_conv_rows(S.hs, S.xn, S.x, L.norm1, sp.layer_norm ? 1 : 0, sp.norm_eps, L.inconv1, L.inconv1_state, n, W, taps, pos0, ctl, st));
+	ST_TRY(stack_linear(*this, c, S.a16, P, ldp, S.hs, W, L.wproj, n, ldp, W, 1.f, st));
+	if (ls.kind == yalm::MixerKind::LatentAttention) {
+		const yalm::MixerSpec &m = ls.mix;
+		const yalm::LatentSpec &a = ls.latent;
+		const int row = a.kv_rank + a.rot_dim, nq = m.heads * (m.dim + a.rot_dim), nqa = m.heads * row, nl = m.heads * a.kv_rank, no = m.heads * m.vdim;
+		const bool own = a.kv_from < 0;
+		ST_TRY(yalm_latent_post_rows(P, ldp, L.o_q, a.q_rank, L.qnorm, L.o_kv, a.kv_rank, a.rot_dim, L.knorm, own ? L.kring : nullptr, L.ring, L.rot_freq,
+		                             L.rot_mag, a.rot.dims, a.rot.interleaved ? 1 : 0, sp.norm_eps, f32, n, pos0, ctl, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.conv, nq, P + L.o_q, ldp, L.wuq, n, nq, a.q_rank, 1.f, st));
+		ST_TRY(yalm_latent_query_rows(S.aux, nqa, S.conv, nq, L.wuk, dt, n, m.heads, m.dim, a.rot_dim, a.kv_rank, L.rot_freq, L.rot_mag, a.rot.dims,
+		                              a.rot.interleaved ? 1 : 0, pos0, ctl, st));
+		// every head reads the one row of a position: keys are whole rows, values their first kv_rank channels
+		ST_TRY(yalm_attn_window_pool_strided(S.scan, nl, S.aux, nqa, L.kring, row, L.kring, row, nullptr, nullptr, S.attn_ws, n, m.heads, 1, row, a.kv_rank,
+		                                     L.ring, 0, m.window, 0, m.scale, f32, c.max_seq_len, pos0, ctl, st));
+		ST_TRY(yalm_head_linear_gate_rows(S.att, no, S.scan, nl, L.wuv, dt, m.out_gate ? P + L.o_gate : nullptr, ldp, n, m.heads, m.vdim, a.kv_rank, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, no, L.wo, n, W, no, 1.f, st));
+	} else {
+		const yalm::GlaSpec &g = ls.gla;
+		const int hd = g.heads * g.dim, hp = g.heads * g.vdim;
+		ST_TRY(stack_linear(*this, c, S.a16, S.aux, hd, P + L.o_a1, ldp, L.wa2, n, hd, g.decay_rank, 1.f, st));
+		ST_TRY(yalm_gla_prep_rows(S.aux, hd, L.d_dt_bias, g.tau, P + L.o_q, ldp, 1.0f / sqrtf((float)g.dim), n, hd, st));
+		ST_TRY(yalm_state_scan_rows(S.scan, hp, P + L.o_k, ldp, P + L.o_q, ldp, P + L.o_v, ldp, S.aux, hd, 1, nullptr, 0, nullptr, 0, nullptr, L.scan_state, n,
+		                            g.heads, 1, g.dim, g.vdim, pos0, ctl, st));
+		ST_TRY(yalm_head_norm_act_rows(S.att, hp, S.scan, hp, P + L.o_gate, ldp, L.mix_norm, n, g.heads, g.vdim, sp.norm_eps, 1, st));
+		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, hp, L.wo, n, W, hp, 1.f, st));
+	}
+	// ---- feed-forward ----
+	const FfnSpec &f = ls.ffn;
+	const float *add_a = S.y1, *add_b = nullptr, *slots = nullptr;
+	int nsum = 0;
+	if (f.kind != FfnSpec::None) {
+		ST_TRY(yalm_residual_sum_rows(S.x, S.y1, nullptr, nullptr, 0, 0, n, W, st));
+		ST_TRY(yalm_norm_conv_rows(S.hs, S.xn, S.x, L.norm2, sp.layer_norm ? 1 : 0, sp.norm_eps, L.inconv2, L.inconv2_state, n, W, taps, pos0, ctl, st));
+		add_a = nullptr;
+		const int act = glu_act_code(f.act);
+		if (f.kind == FfnSpec::Dense) {
+			ST_TRY(stack_linear(*this, c, S.a16, S.gu, 2 * f.ff, S.hs, W, L.wgu, n, 2 * f.ff, W, 1.f, st));
+			ST_TRY(yalm_glu_act_rows(S.h, S.gu, n, f.ff, act, f.act_alpha, f.limit, f.up_offset, st));
+			ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.h, f.ff, L.wdown, n, W, f.ff, 1.f, st));
+			add_a = S.y1;
+		} else {
+			const int EA = f.experts + f.identity;
+			if (f.shared_ff > 0) { // before the routed experts: the grouped route waits on the host for the chosen experts
+				ST_TRY(stack_linear(*this, c, S.a16, S.gu, 2 * f.shared_ff, S.hs, W, L.wsgu, n, 2 * f.shared_ff, W, 1.f, st));
+				ST_TRY(yalm_glu_act_rows(S.h, S.gu, n, f.shared_ff, glu_act_code(f.shared_act), 1.f, 0.f, 0.f, st));
+				ST_TRY(stack_linear(*this, c, S.a16, S.y2, W, S.h, f.shared_ff, L.wsdown, n, W, f.shared_ff, 1.f, st));
+				add_b = S.y2;
+			}
+			ST_TRY(yalm_router_bias_topk_rows(S.ids, S.wts, S.hs, W, L.router, dt, n, EA, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
+			                                  f.renormalize ? 1 : 0, f.renorm_eps, 1, 1, f.choice_bias ? L.router_bias : nullptr, f.router_scale, st));
+			if (S.moe_gu && !ctl && f.experts > 0 && n * f.top >= 64 && W % 8 == 0 && f.ff % 8 == 0 && !moe_grouped_off())
+				ST_TRY(stack_moe_grouped(S, L, S.hs, S.a16, n, act, st));
+			else {
+				if (f.experts > 0)
+					ST_TRY(yalm_moe_glu_slots_real(S.h, S.hs, W, L.wg, L.wu, dt, S.ids, S.wts, n, f.top, f.ff, W, act, f.act_alpha, f.limit, f.up_offset,
+					                               f.weight_on_input ? 1 : 0, f.experts, st));
+				ST_TRY(yalm_moe_down_slots_real(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, f.experts, S.hs, W, st));
+			}
+			slots = S.y, nsum = f.top;
+		}
+	}
+	// the layer's result (x + what is still to be added) joins the earlier ones; x becomes their weighted sum
+	if (sp.depth_average)
+		return yalm_depth_average_rows(S.x, S.hist, (size_t)S.cap * W, L.depth_w, index + 2, n, W, add_a, add_b, slots, W, nsum, st);
+	return yalm_residual_sum_rows(S.x, add_a, add_b, slots, W, nsum, n, W, st);
+}
+
 int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_want) {
 	const Config &c = *config;
 	const StackSpec &sp = *c.stack;
@@ -717,6 +928,7 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 	const float woff = sp.norm_one_plus ? 1.f : 0.f;
 	ST_TRY(yalm_embed_rows(S.x, token_embedding_table, _pos_table, dt, from_ctl ? nullptr : S.tokens, n, W, pos0, ctl, sp.embed_scale, st));
 	if (sp.embed_norm) ST_TRY(yalm_norm_shift_rows(S.x, nullptr, S.x, _embed_norm, sp.norm_scalar, woff, sp.norm_eps, nullptr, nullptr, n, W, pos0, ctl, st));
+	if (sp.depth_average) ST_TRY(yalm_depth_average_rows(S.x, S.hist, (size_t)S.cap * W, nullptr, 1, n, W, nullptr, nullptr, nullptr, 0, 0, st)); // slab 0: the embedding output
 	int layer_no = 0;
 	auto tap = [&]() -> int { // tests: the residual rows after this layer
 		if (_stack_tap && !from_ctl) {
@@ -730,6 +942,11 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 		const StackLayer &L = *Lp;
 		if (sp.parallel_block) {
 			ST_TRY(stack_layer_parallel(S, L, n, pos0, ctl, st));
+			ST_TRY(tap());
+			continue;
+		}
+		if (own_state(L)) {
+			ST_TRY(stack_layer_prenorm(S, L, layer_no, n, pos0, ctl, st));
 			ST_TRY(tap());
 			continue;
 		}
@@ -787,6 +1004,8 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 		ST_TRY(tap());
 	}
 	if (n_want > 0) {
+		if (sp.layer_norm) ST_TRY(yalm_layer_norm_gather_rows(S.xn, S.x, from_ctl ? nullptr : S.want, rms_final_weight, 1, sp.norm_eps, n_want, W, st));
+		else
 		ST_TRY(yalm_norm_gather_rows(S.xn, S.x, from_ctl ? nullptr : S.want, rms_final_weight, sp.norm_scalar, woff, sp.norm_eps, n_want, W, st));
 		// a single wanted row lands directly where the samplers read it
 		float *dst = n_want == 1 ? s.logits_dev() : S.logits;

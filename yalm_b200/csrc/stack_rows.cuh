@@ -63,6 +63,7 @@ __device__ __forceinline__ float glu_value(float g, float u, int act, float alph
 	if (limit > 0.f) g = fminf(g, limit), u = fminf(fmaxf(u, -limit), limit);
 	float a;
 	if (act == 2) a = g / (1.0f + expf(-alpha * g));      // g * sigmoid(alpha g)
+	else if (act == 3) a = 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g))); // tanh GELU, sqrt(2 / pi) to fp32 precision
 	else if (act == YALM_ACT_SILU) a = act_silu(g);
 	else a = act_gelu(g);
 	return a * (u + up_offset);
