@@ -48,6 +48,7 @@ WORKLOADS = {
     # the layered design at model-like sizes beside the equal-size .yalm block (yalm_b200/stack_bench.py): prefill and decode, one line
     "retezen-sizes": ("tiny", "bf16", 4096, "Retezen (windowed attention with pooled blocks, dense / routed feed-forward) at model-like sizes"),
     "fapudra-sizes": ("tiny", "bf16", 4096, "Fapudra (parallel blocks: state-space / sigmoid attention + gated delta rule, routed experts) at model-like sizes"),
+    "fegizen-sizes": ("tiny", "bf16", 4096, "Fegizen (latent attention over cached latents / gated linear attention, experts with identity and shared experts) at model-like sizes"),
     "mistral-7b-fp16-prefill": ("mistral-7b", "fp16", 4096, "Mistral-7B-v0.2 fp16 random-init, 4096-token prompt hydrated in 512-token chunks (tcgen05 GEMMs)"),
 }
 HEADLINE = "mistral-7b-fp16-4k"
@@ -368,6 +369,11 @@ def main():
             raise SystemExit("bench.py: the layered models run on one GPU")
         from yalm_b200 import stack_bench
         return stack_bench.run_fapudra(args, base, _emit, shm_path, ClockSampler)
+    if args.workload == "fegizen-sizes":
+        if world > 1:
+            raise SystemExit("bench.py: the layered models run on one GPU")
+        from yalm_b200 import stack_bench
+        return stack_bench.run_fegizen(args, base, _emit, shm_path, ClockSampler)
     if args.workload.endswith("-prefill"):
         if world > 1:
             raise SystemExit("bench.py: the prefill workload is single-GPU")

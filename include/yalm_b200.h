@@ -315,6 +315,9 @@ int yalm_softcap_rows(float *z, int n, int dim, float cap, yalm_stream_t s);
  * replaced by the call's last ones. */
 int yalm_norm_conv_rows(float *u, float *h, const float *x, const float *w, int layer_norm, float eps, const float *conv_w, float *state, int n,
                         int dim, int taps, int pos0, const int *ctl, yalm_stream_t s);
+/* yalm_norm_conv_rows after x += add (add optional). */
+int yalm_add_norm_conv_rows(float *u, float *h, float *x, const float *add, const float *w, int layer_norm, float eps, const float *conv_w,
+                            float *state, int n, int dim, int taps, int pos0, const int *ctl, yalm_stream_t s);
 /* Rotary table: freq (rot_dims / 2) fp32 and a magnitude on cos and sin; interleaved != 0: pair i = channels (2 i, 2 i + 1).
  * yalm_latent_post_rows: row m of proj (ld): [o_q, +q_rank) RMS-normed with q_norm in place; ring_buf != NULL: [o_kv, +kv_rank) RMS-normed
  * with kv_norm and [o_kv + kv_rank, +rot_dim) with its first rot_dims channels rotated go to ring row p % ring as
@@ -327,6 +330,18 @@ int yalm_latent_post_rows(float *proj, int ld, int o_q, int q_rank, const float 
 int yalm_latent_query_rows(float *out, int ldo, const float *q, int ldq, const void *uk, int dtype, int n, int heads, int dim, int rot_dim,
                            int kv_rank, const float *freq, float magnitude, int rot_dims, int interleaved, int pos0, const int *ctl,
                            yalm_stream_t s);
+/* Prompt portions of latent attention on the tensor cores: the cached rows (bf16) of positions first_pos .. first_pos + count - 1
+ * give (a) their latents as a dense bf16 operand (count, kv_rank) and, with kv (count, heads (dim + vdim)) fp32 = that operand times
+ * [W_uk ; W_uv]^T, (b) per head the key [unrotated | rotated key part] and the value as bf16 rows of head-major rings
+ * (head, ring_out, dim + rot_dim | vdim), slot = position % ring_out: what yalm_attn_window_pool_mma reads. */
+int yalm_latent_gather_rows16(void *out16, const void *ring_buf, int ring, int row, int kv_rank, int first_pos, int count, yalm_stream_t s);
+int yalm_latent_pack_rings(void *key_ring, void *value_ring, const float *kv, int ldkv, const void *ring_buf, int ring, int kv_rank, int rot_dim,
+                           int heads, int dim, int vdim, int ring_out, int first_pos, int count, yalm_stream_t s);
+/* In place: channels [offset, offset + rot_dims) of every head (head_size channels) of row m turned by its position. */
+int yalm_rotate_heads_rows(float *q, int ldq, int heads, int head_size, int offset, const float *freq, float magnitude, int rot_dims,
+                           int interleaved, int n, int pos0, const int *ctl, yalm_stream_t s);
+/* x[m, :dim] *= sigmoid(gate[m, :dim]) */
+int yalm_sigmoid_gate_rows(float *x, int ldx, const float *gate, int ldg, int n, int dim, yalm_stream_t s);
 /* out[m, h, :N] = w_h x[m, h, :K] (w (heads N, K)), times sigmoid(gate[m, h, :N]) if gate. */
 int yalm_head_linear_gate_rows(float *out, int ldo, const float *x, int ldx, const void *w, int dtype, const float *gate, int ldg, int n, int heads,
                                int N, int K, yalm_stream_t s);
@@ -354,6 +369,8 @@ int yalm_router_bias_topk_rows(int *ids, float *wts, const float *x, int ldx, co
 /* The slot kernels with identity experts: ids >= n_real have no matrices; their slot returns the row of x (times the weight). */
 int yalm_moe_glu_slots_real(float *h, const float *x, int ldx, const void *wg, const void *wu, int dtype, const int *ids, const float *wts, int n,
                             int top, int ff, int dim, int act, float alpha, float limit, float up_offset, int in_scale, int n_real, yalm_stream_t s);
+int yalm_moe_identity_slots(float *y, int ldy, const float *x, int ldx, const int *ids, const float *wts, int n, int top, int dim, int n_real,
+                            int out_scale, yalm_stream_t s);
 int yalm_moe_down_slots_real(float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int n, int top, int ff,
                              int dim, int out_scale, int n_real, const float *x, int ldx, yalm_stream_t s);
 

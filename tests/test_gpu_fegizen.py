@@ -499,9 +499,9 @@ def test_prompt_portions_on_the_tensor_cores_and_serving_precision(tmp_path):
     """Widths and portions large enough for the tensor-core products and the grouped experts; bf16 against the float64 run by
     row-wise quantiles (a rounded router input may flip a close choice), and whole = decoded in bf16."""
     cfg = O.make_config([
-        ("latent_attention", O.latent_mixer(heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=48, window=50), O.moe_mlp(ff=64, experts=6, identity=2, top=2, shared=32)),
+        ("latent_attention", O.latent_mixer(heads=4, dim=48, rot_dim=16, vdim=32, kv_rank=64, q_rank=48, window=50), O.moe_mlp(ff=64, experts=6, identity=2, top=2, shared=32)),
         ("gla", O.gla_mixer(heads=2, dim=32, vdim=64), O.dense_mlp(ff=128)),
-        ("latent_attention", O.latent_mixer(heads=4, dim=32, rot_dim=16, vdim=32, kv_rank=64, q_rank=48, window=20, kv_from=0), O.moe_mlp(ff=64, experts=6, identity=2, top=2, shared=32)),
+        ("latent_attention", O.latent_mixer(heads=2, dim=112, rot_dim=16, vdim=64, kv_rank=64, q_rank=48, window=20, kv_from=0), O.moe_mlp(ff=64, experts=6, identity=2, top=2, shared=32)),
     ], width=128, vocab=160)
     folder, W = checkpoint(tmp_path, cfg, seed=10, a_rank=8, router_gain=6.0)
     T = 150

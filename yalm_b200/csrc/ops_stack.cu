@@ -30,40 +30,6 @@
 namespace yalm {
 namespace stack {
 
-// dot(weight row, x) over K elements, result in every lane.  `vec`: the row and x are 16-byte aligned and K % VEC == 0.
-template <int DT>
-__device__ __forceinline__ float warp_dot(const void *w, size_t row_off, const float *__restrict__ x, int K, bool vec) {
-	using E = Elem<DT>;
-	const int lane = threadIdx.x & 31;
-	float acc = 0.f;
-	if (vec) {
-		const typename E::T *row = static_cast<const typename E::T *>(w) + row_off;
-		constexpr int U = 4, STEP = 32 * E::VEC; // U loads in flight per lane before the first multiply
-		for (int k0 = lane * E::VEC; k0 < K; k0 += U * STEP) {
-			uint4 wv[U];
-#pragma unroll
-			for (int u = 0; u < U; ++u)
-				if (k0 + u * STEP < K) wv[u] = ldg_stream(row + k0 + u * STEP);
-#pragma unroll
-			for (int u = 0; u < U; ++u)
-				if (k0 + u * STEP < K) {
-					float f[8];
-					E::unpack(wv[u], f);
-					const int k = k0 + u * STEP;
-#pragma unroll
-					for (int i = 0; i < E::VEC; i += 4) {
-						const float4 xv = *reinterpret_cast<const float4 *>(x + k + i);
-						acc = fmaf(f[i], xv.x, acc), acc = fmaf(f[i + 1], xv.y, acc), acc = fmaf(f[i + 2], xv.z, acc), acc = fmaf(f[i + 3], xv.w, acc);
-					}
-				}
-		}
-	} else {
-		for (int k = lane; k < K; k += 32) acc = fmaf(E::get(w, row_off + k), x[k], acc);
-	}
-	return warp_sum(acc);
-}
-
-
 // ---- embedding ---------------------------------------------------------------------------------------------------------
 template <int DT>
 __global__ void embed_rows_kernel(float *__restrict__ x, const void *__restrict__ table, const void *__restrict__ positions,
@@ -743,6 +709,15 @@ __global__ void __launch_bounds__(128) moe_down_slots_kernel(float *__restrict__
 	if ((threadIdx.x & 31) == 0) y[(size_t)s * ldy + n] = v;
 }
 
+// Slots of identity experts (ids >= n_real): y[s] = the slot's row of x (times its weight if out_scale).  One CTA per slot.
+__global__ void moe_identity_slots_kernel(float *__restrict__ y, int ldy, const float *__restrict__ x, int ldx, const int *__restrict__ ids,
+                                          const float *__restrict__ wts, int top, int dim, int n_real, int out_scale) {
+	const int s = blockIdx.x;
+	if (ids[s] < n_real) return;
+	const float w = out_scale ? wts[s] : 1.f;
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) y[(size_t)s * ldy + e] = x[(size_t)(s / top) * ldx + e] * w;
+}
+
 // ---- experts, rows grouped by expert (prompt portions on the tensor cores) ---------------------------------------------------
 // order[j]: the slot (row * top + k) that sits at place j once the slots are sorted by expert.  out16[j, :] = the slot's row
 // of x, times the slot's weight when the weight multiplies the expert's input, rounded to the 16-bit operand type.
@@ -1007,6 +982,13 @@ extern "C" int yalm_moe_down_slots_real(float *y, int ldy, const float *h, const
 	if (!y || !h || !wd || !ids || !wts || n < 1 || top < 1 || (n_real < (1 << 30) && !x)) return YALM_EINVAL;
 	const bool vec = row_vec(wd, ff, dtype) && aligned16(h) && ff % 4 == 0;
 	DISPATCH_DT(dtype, (moe_down_slots_kernel<DT><<<dim3((dim + 3) / 4, n * top), 128, 0, (cudaStream_t)s>>>(y, ldy, h, wd, ids, wts, ff, dim, out_scale, vec, n_real, x, ldx, top)));
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_moe_identity_slots(float *y, int ldy, const float *x, int ldx, const int *ids, const float *wts, int n, int top, int dim, int n_real,
+                                       int out_scale, yalm_stream_t s) {
+	if (!y || !x || !ids || !wts || n < 1 || top < 1 || dim < 1) return YALM_EINVAL;
+	moe_identity_slots_kernel<<<n * top, 256, 0, (cudaStream_t)s>>>(y, ldy, x, ldx, ids, wts, top, dim, n_real, out_scale);
 	return (int)cudaGetLastError();
 }
 

@@ -17,6 +17,8 @@
 
 #include <cuda_bf16.h>
 
+#include <algorithm>
+
 #include "launch.h"
 #include "stack_rows.cuh"
 
@@ -55,10 +57,15 @@ __device__ __forceinline__ void normed_row(float *dst, const float *__restrict__
 // h_m also goes to h.  single != 0 (one-row calls): the CTA then shifts the state itself.
 __global__ void __launch_bounds__(256) norm_conv_rows_kernel(float *__restrict__ u, float *__restrict__ h, const float *__restrict__ x,
                                                              const float *__restrict__ w, int layer_norm, float eps, const float *__restrict__ cw,
-                                                             float *state, int dim, int taps, int single, int pos0, const int *__restrict__ ctl) {
+                                                             float *state, int dim, int taps, int single, int pos0, const int *__restrict__ ctl,
+                                                             float *xadd, const float *__restrict__ add) {
 	extern __shared__ float hs[]; // taps x dim
 	__shared__ float red[33];
 	const int m = blockIdx.x, p0 = first_pos(ctl, pos0);
+	if (add) { // one-row calls: the residual takes the previous sublayer's output first
+		for (int e = threadIdx.x; e < dim; e += blockDim.x) xadd[e] += add[e];
+		__syncthreads();
+	}
 	for (int j = 0; j < taps; ++j) normed_row(hs + (size_t)j * dim, x, w, state, m - (taps - 1) + j, p0, taps, dim, layer_norm, eps, red);
 	__syncthreads();
 	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
@@ -138,7 +145,7 @@ __global__ void __launch_bounds__(256) latent_post_rows_kernel(float *__restrict
 // weights.
 constexpr int kLqRows = 8;
 template <int DT>
-__global__ void __launch_bounds__(128) latent_query_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+__global__ void __launch_bounds__(64) latent_query_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
                                                                 const void *__restrict__ uk, int n, int dim, int rot_dim, int kv_rank,
                                                                 const float *__restrict__ freq, float mag, int rot_dims, int interleaved, int pos0,
                                                                 const int *__restrict__ ctl) {
@@ -150,7 +157,8 @@ __global__ void __launch_bounds__(128) latent_query_rows_kernel(float *__restric
 	}
 	__syncthreads();
 	const size_t obase = (size_t)h * (kv_rank + rot_dim);
-	for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) {
+	// grid.z cuts the output channels into pieces of one per thread: a decode row then still fills the GPU
+	for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < kv_rank; c += gridDim.z * blockDim.x) {
 		float acc[kLqRows];
 #pragma unroll
 		for (int i = 0; i < kLqRows; ++i) acc[i] = 0.f;
@@ -164,6 +172,7 @@ __global__ void __launch_bounds__(128) latent_query_rows_kernel(float *__restric
 			if (i < mb) out[(size_t)(m0 + i) * ldo + obase + c] = acc[i];
 	}
 	const int half = rot_dims / 2;
+	if (blockIdx.z) return;
 	for (int e = threadIdx.x; e < mb * rot_dim; e += blockDim.x) {
 		const int i = e / rot_dim, j = e % rot_dim;
 		const float *qr = qs + i * dq + dim;
@@ -185,7 +194,7 @@ template <int DT>
 __global__ void __launch_bounds__(256) head_linear_gate_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ x, int ldx,
                                                                     const void *__restrict__ w, const float *__restrict__ gate, int ldg, int n, int N,
                                                                     int K) {
-	extern __shared__ float xs[]; // kHlRows x K
+	extern __shared__ __align__(16) float xs[]; // kHlRows x K
 	const int h = blockIdx.x, m0 = blockIdx.y * kHlRows, mb = min(kHlRows, n - m0);
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	for (int e = threadIdx.x; e < kHlRows * K; e += blockDim.x) {
@@ -193,7 +202,19 @@ __global__ void __launch_bounds__(256) head_linear_gate_rows_kernel(float *__res
 		xs[e] = i < mb ? x[(size_t)(m0 + i) * ldx + (size_t)h * K + c] : 0.f;
 	}
 	__syncthreads();
-	for (int j = warp; j < N; j += 8) {
+	const bool vec = K % Elem<DT>::VEC == 0 && aligned16(w) && ((size_t)K * sizeof(typename Elem<DT>::T)) % 16 == 0;
+	if (mb <= 2 && vec) { // decode rows: 16-byte weight loads, several in flight per lane, one row at a time
+		for (int j = blockIdx.z * 8 + warp; j < N; j += gridDim.z * 8)
+			for (int i = 0; i < mb; ++i) {
+				const float v = warp_dot<DT>(w, ((size_t)h * N + j) * K, xs + i * K, K, true);
+				if (lane == 0) {
+					const size_t o = (size_t)(m0 + i) * ldo + (size_t)h * N + j;
+					out[o] = gate ? v / (1.0f + expf(-gate[(size_t)(m0 + i) * ldg + (size_t)h * N + j])) : v;
+				}
+			}
+		return;
+	}
+	for (int j = blockIdx.z * 8 + warp; j < N; j += gridDim.z * 8) {
 		float acc[kHlRows];
 #pragma unroll
 		for (int i = 0; i < kHlRows; ++i) acc[i] = 0.f;
@@ -252,6 +273,54 @@ __global__ void depth_average_rows_kernel(float *__restrict__ x, float *__restri
 	x[i] = v;
 }
 
+// ---- latent attention, prompt portions: keys and values written out per head for the tensor-core attention -------------------
+// The cached rows of positions first .. first + count - 1 (bf16 ring, row = [latent | key part], slot = position % ring):
+// their latents as one dense bf16 operand (count, kv_rank) ...
+__global__ void latent_gather_rows_kernel(__nv_bfloat16 *__restrict__ out, const __nv_bfloat16 *__restrict__ ring_buf, int ring, int row, int kv_rank,
+                                          int first) {
+	const int j = blockIdx.x;
+	const __nv_bfloat16 *src = ring_buf + (size_t)((first + j) % ring) * row;
+	for (int e = threadIdx.x; e < kv_rank; e += blockDim.x) out[(size_t)j * kv_rank + e] = src[e];
+}
+// ... and, from kv (count, heads (dim + vdim)) = latents x [W_uk ; W_uv]^T (fp32: all heads' unrotated keys, then all heads' values),
+// per head the key [unrotated | the row's rotated key part] and the value, as bf16 rows of head-major rings (head, slot, channel)
+// with slot = position % ring_out: what the windowed tensor-core attention reads.
+__global__ void __launch_bounds__(256) latent_pack_rings_kernel(__nv_bfloat16 *__restrict__ kout, __nv_bfloat16 *__restrict__ vout,
+                                                                const float *__restrict__ kv, int ldkv, const __nv_bfloat16 *__restrict__ ring_buf,
+                                                                int ring, int row, int kv_rank, int rot_dim, int heads, int dim, int vdim, int ring_out,
+                                                                int first) {
+	const int j = blockIdx.x, p = first + j, dk = dim + rot_dim;
+	const float *src = kv + (size_t)j * ldkv;
+	const __nv_bfloat16 *kr = ring_buf + (size_t)(p % ring) * row + kv_rank;
+	const size_t slot = (size_t)(p % ring_out);
+	for (int e = threadIdx.x; e < heads * dk; e += blockDim.x) {
+		const int h = e / dk, d = e % dk;
+		kout[((size_t)h * ring_out + slot) * dk + d] = d < dim ? __float2bfloat16_rn(src[h * dim + d]) : kr[d - dim];
+	}
+	for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) {
+		const int h = e / vdim, d = e % vdim;
+		vout[((size_t)h * ring_out + slot) * vdim + d] = __float2bfloat16_rn(src[heads * dim + e]);
+	}
+}
+// In place: channels [offset, offset + rot_dims) of every head (head_size channels each) of row m turned by position p0 + m.
+__global__ void rotate_heads_rows_kernel(float *__restrict__ q, int ldq, int heads, int head_size, int offset, const float *__restrict__ freq, float mag,
+                                         int rot_dims, int interleaved, int pos0, const int *__restrict__ ctl) {
+	const int m = blockIdx.x, p = first_pos(ctl, pos0) + m, half = rot_dims / 2;
+	for (int e = threadIdx.x; e < heads * half; e += blockDim.x) {
+		const int h = e / half, i = e % half;
+		float *v = q + (size_t)m * ldq + (size_t)h * head_size + offset;
+		const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+		float a, b;
+		rotate_pair(v[ia], v[ib], p, freq[i], mag, &a, &b);
+		v[ia] = a, v[ib] = b;
+	}
+}
+// x[m, :dim] *= sigmoid(gate[m, :dim])
+__global__ void sigmoid_gate_rows_kernel(float *__restrict__ x, int ldx, const float *__restrict__ gate, int ldg, int dim) {
+	const int m = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x;
+	if (e < dim) x[(size_t)m * ldx + e] /= 1.0f + expf(-gate[(size_t)m * ldg + e]);
+}
+
 // out[r] = layer norm (or RMS norm) of x[rows[r]] times w   (rows null: r itself)
 __global__ void __launch_bounds__(256) layer_norm_gather_rows_kernel(float *__restrict__ out, const float *__restrict__ x, const int *__restrict__ rows,
                                                                      const float *__restrict__ w, int layer_norm, float eps, int dim) {
@@ -290,12 +359,23 @@ using namespace yalm::stack;
 
 extern "C" int yalm_norm_conv_rows(float *u, float *h, const float *x, const float *w, int layer_norm, float eps, const float *conv_w, float *state, int n,
                                    int dim, int taps, int pos0, const int *ctl, yalm_stream_t s) {
+	return yalm_add_norm_conv_rows(u, h, const_cast<float *>(x), nullptr, w, layer_norm, eps, conv_w, state, n, dim, taps, pos0, ctl, s);
+}
+
+// The same after x += add (add optional; one launch for one-row calls, a launch of its own before the norm otherwise: a row's
+// CTA also reads the rows before it).
+extern "C" int yalm_add_norm_conv_rows(float *u, float *h, float *x, const float *add, const float *w, int layer_norm, float eps, const float *conv_w,
+                                       float *state, int n, int dim, int taps, int pos0, const int *ctl, yalm_stream_t s) {
+	if (add && n > 1) {
+		if (int rc = yalm_residual_sum_rows(x, add, nullptr, nullptr, 0, 0, n, dim, s)) return rc;
+		add = nullptr;
+	}
 	if (!u || !h || !x || !w || !conv_w || n < 1 || dim < 1 || taps < 1 || (taps > 1 && !state) || u == x || h == x) return YALM_EINVAL;
 	const size_t smem = sizeof(float) * (size_t)taps * dim;
 	if (smem > 160 * 1024) return YALM_EINVAL;
 	cudaStream_t st = (cudaStream_t)s;
 	if (smem > 48 * 1024) YALM_TRY(cudaFuncSetAttribute(norm_conv_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-	norm_conv_rows_kernel<<<n, 256, smem, st>>>(u, h, x, w, layer_norm, eps, conv_w, state, dim, taps, n == 1, pos0, ctl);
+	norm_conv_rows_kernel<<<n, 256, smem, st>>>(u, h, x, w, layer_norm, eps, conv_w, state, dim, taps, n == 1, pos0, ctl, x, add);
 	if (n > 1 && taps > 1) norm_conv_state_kernel<<<(dim + 255) / 256, 256, 0, st>>>(state, h, n, dim, taps, pos0, ctl);
 	return (int)cudaGetLastError();
 }
@@ -324,8 +404,8 @@ extern "C" int yalm_latent_query_rows(float *out, int ldo, const float *q, int l
 		return YALM_EINVAL;
 	const size_t smem = sizeof(float) * kLqRows * (size_t)(dim + rot_dim);
 	if (smem > 48 * 1024) return YALM_EINVAL;
-	const dim3 grid(heads, (n + kLqRows - 1) / kLqRows);
-	DISPATCH_DT(dtype, (latent_query_rows_kernel<DT><<<grid, 128, smem, (cudaStream_t)s>>>(out, ldo, q, ldq, uk, n, dim, rot_dim, kv_rank, freq, magnitude,
+	const dim3 grid(heads, (n + kLqRows - 1) / kLqRows, (kv_rank + 63) / 64);
+	DISPATCH_DT(dtype, (latent_query_rows_kernel<DT><<<grid, 64, smem, (cudaStream_t)s>>>(out, ldo, q, ldq, uk, n, dim, rot_dim, kv_rank, freq, magnitude,
 	                                                                                      rot_dims, interleaved, pos0, ctl)));
 	return (int)cudaGetLastError();
 }
@@ -335,7 +415,8 @@ extern "C" int yalm_head_linear_gate_rows(float *out, int ldo, const float *x, i
 	if (!out || !x || !w || n < 1 || heads < 1 || N < 1 || K < 1) return YALM_EINVAL;
 	const size_t smem = sizeof(float) * kHlRows * (size_t)K;
 	if (smem > 48 * 1024) return YALM_EINVAL;
-	const dim3 grid(heads, (n + kHlRows - 1) / kHlRows);
+	const int rb = (n + kHlRows - 1) / kHlRows;
+	const dim3 grid(heads, rb, heads * rb >= 296 ? 1 : std::min((N + 7) / 8, (296 + heads * rb - 1) / (heads * rb))); // few rows: the outputs spread over more CTAs
 	DISPATCH_DT(dtype, (head_linear_gate_rows_kernel<DT><<<grid, 256, smem, (cudaStream_t)s>>>(out, ldo, x, ldx, w, gate, ldg, n, N, K)));
 	return (int)cudaGetLastError();
 }
@@ -358,5 +439,36 @@ extern "C" int yalm_layer_norm_gather_rows(float *out, const float *x, const int
                                            yalm_stream_t s) {
 	if (!out || !x || !w || n_rows < 1 || dim < 1) return YALM_EINVAL;
 	layer_norm_gather_rows_kernel<<<n_rows, 256, 0, (cudaStream_t)s>>>(out, x, rows, w, layer_norm, eps, dim);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_latent_gather_rows16(void *out16, const void *ring_buf, int ring, int row, int kv_rank, int first_pos, int count, yalm_stream_t s) {
+	if (!out16 || !ring_buf || ring < 1 || kv_rank < 1 || row < kv_rank || first_pos < 0 || count < 1 || count > ring) return YALM_EINVAL;
+	latent_gather_rows_kernel<<<count, 128, 0, (cudaStream_t)s>>>((__nv_bfloat16 *)out16, (const __nv_bfloat16 *)ring_buf, ring, row, kv_rank, first_pos);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_latent_pack_rings(void *key_ring, void *value_ring, const float *kv, int ldkv, const void *ring_buf, int ring, int kv_rank, int rot_dim,
+                                      int heads, int dim, int vdim, int ring_out, int first_pos, int count, yalm_stream_t s) {
+	if (!key_ring || !value_ring || !kv || !ring_buf || ring < 1 || ring_out < 1 || heads < 1 || dim < 0 || vdim < 1 || first_pos < 0 || count < 1 ||
+	    count > ring || count > ring_out)
+		return YALM_EINVAL;
+	latent_pack_rings_kernel<<<count, 256, 0, (cudaStream_t)s>>>((__nv_bfloat16 *)key_ring, (__nv_bfloat16 *)value_ring, kv, ldkv,
+	                                                             (const __nv_bfloat16 *)ring_buf, ring, kv_rank + rot_dim, kv_rank, rot_dim, heads, dim, vdim,
+	                                                             ring_out, first_pos);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_rotate_heads_rows(float *q, int ldq, int heads, int head_size, int offset, const float *freq, float magnitude, int rot_dims,
+                                      int interleaved, int n, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!q || n < 1 || heads < 1 || rot_dims < 0 || rot_dims % 2 || offset < 0 || offset + rot_dims > head_size || (rot_dims > 0 && !freq)) return YALM_EINVAL;
+	if (rot_dims == 0) return 0;
+	rotate_heads_rows_kernel<<<n, 128, 0, (cudaStream_t)s>>>(q, ldq, heads, head_size, offset, freq, magnitude, rot_dims, interleaved, pos0, ctl);
+	return (int)cudaGetLastError();
+}
+
+extern "C" int yalm_sigmoid_gate_rows(float *x, int ldx, const float *gate, int ldg, int n, int dim, yalm_stream_t s) {
+	if (!x || !gate || n < 1 || dim < 1) return YALM_EINVAL;
+	sigmoid_gate_rows_kernel<<<dim3((dim + 255) / 256, n), 256, 0, (cudaStream_t)s>>>(x, ldx, gate, ldg, dim);
 	return (int)cudaGetLastError();
 }

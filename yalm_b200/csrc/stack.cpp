@@ -231,7 +231,10 @@ struct Model::StackScratch {
 	      *logits = nullptr, *probs = nullptr;
 	void *a16 = nullptr, *a16e = nullptr, *a16r = nullptr; // 16-bit operands of the tensor-core products: main stream, experts' stream, second mixer's stream
 	float *hs = nullptr, *conv = nullptr, *aux = nullptr, *scan = nullptr, *att2 = nullptr, *y1 = nullptr, *y2 = nullptr; // parallel blocks
+	float *hsh = nullptr;     // the shared expert's hidden rows (the routed experts' are in h)
 	float *hist = nullptr;    // weighted sum over depth: the embedding output and every layer's result of the current rows, (layers + 1, cap, width)
+	void *lat16 = nullptr, *lat_ek = nullptr, *lat_ev = nullptr; // latent attention, prompt portions: latents of the visible rows (bf16), keys / values per head
+	float *latkv = nullptr;
 	float *attn_ws = nullptr; // split partials of decode-sized attention calls
 	int *ids = nullptr, *tokens = nullptr, *want = nullptr, *targets = nullptr;
 	float *moe_gu = nullptr, *moe_ys = nullptr; // experts on the tensor cores: (gate | up) and down outputs of the slots sorted by expert
@@ -404,8 +407,11 @@ void Model::build_stack(YALMData &data) {
 				pl.push_back({(void **)&L->qnorm, {vec32(tensor(i, TensorRole::LatentDqNorm, -1, {a.q_rank}))}});
 				if (own) pl.push_back({(void **)&L->knorm, {vec32(tensor(i, TensorRole::LatentDkvNorm, -1, {a.kv_rank}))}});
 				pl.push_back({&L->wuq, {mat(tensor(i, TensorRole::LatentUq, -1, {m.heads * (m.dim + a.rot_dim), a.q_rank}))}});
-				if (m.dim > 0) pl.push_back({&L->wuk, {mat(tensor(i, TensorRole::LatentUk, -1, {m.heads * m.dim, a.kv_rank}))}});
-				pl.push_back({&L->wuv, {mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
+				// W_uk then W_uv in one piece: prompt portions multiply the cached latents by both at once
+				if (m.dim > 0)
+					pl.push_back({&L->wuk, {mat(tensor(i, TensorRole::LatentUk, -1, {m.heads * m.dim, a.kv_rank})), mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
+				else
+					pl.push_back({&L->wuv, {mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
 				pl.push_back({&L->wo, {mat(tensor(i, TensorRole::Wo, -1, {W, no}))}});
 				if (a.rot.dims > 0) {
 					std::vector<float> fr;
@@ -589,8 +595,21 @@ void Model::cuda_stack(int device) {
 	for (auto &L : _stack) side_bufs = side_bufs || own_state(*L);
 	for (auto &L : _stack) // a layer that reads another layer's cache rows
 		if (L->kv_owner >= 0 && L->kv_owner < (int)_stack.size() && !L->kring) L->kring = _stack[L->kv_owner]->kring, L->ring = _stack[L->kv_owner]->ring;
+	// latent attention, prompt portions in 16-bit: the window's latents as one operand, their keys and values per head as rings
+	size_t lat16 = 0, latkv = 0, lat_ek = 0, lat_ev = 0;
+	for (auto &L : _stack) {
+		const yalm::LayerSpec &ls = L->spec;
+		if (ls.kind != yalm::MixerKind::LatentAttention) continue;
+		if (ls.mix.dim > 0 && !L->wuv) L->wuv = static_cast<char *>(L->wuk) + (size_t)ls.mix.heads * ls.mix.dim * ls.latent.kv_rank * dtype_size(c.weight_dtype);
+		if (c.weight_dtype == DType::F32 || ls.mix.window < 1) continue;
+		const size_t rows = std::min<size_t>(L->ring, (size_t)ls.mix.window + c.stack_chunk), H = ls.mix.heads;
+		lat16 = std::max(lat16, rows * ls.latent.kv_rank * 2), latkv = std::max(latkv, rows * H * (ls.mix.dim + ls.mix.vdim) * 4);
+		lat_ek = std::max(lat_ek, H * L->ring * (ls.mix.dim + ls.latent.rot_dim) * 2), lat_ev = std::max(lat_ev, H * L->ring * ls.mix.vdim * 2);
+	}
 	const size_t pb = side_bufs ? 1 : 0, nconv = std::max(1, s.max_conv()), naux = std::max(1, s.max_aux()), no = std::max(1, s.max_o_dim());
 	const size_t kmax = std::max({W, (size_t)s.max_o_dim(), ff});
+	size_t shared_ff = 0;
+	for (const LayerSpec &l : s.layers) shared_ff = std::max<size_t>(shared_ff, l.ffn.shared_ff);
 	const bool moe = s.max_experts() > 0 && c.weight_dtype != DType::F32; // the grouped route needs 16-bit operands
 	auto pad = [](size_t b) { return (b + 255) / 256 * 256; };
 	struct Slot {
@@ -605,7 +624,8 @@ void Model::cuda_stack(int device) {
 	             {(void **)&S.attn_ws, 4 * yalm_attn_window_pool_workspace(512)}, {(void **)&S.ticket, 256},
 	             {(void **)&S.hs, pb * 4 * cap * W}, {(void **)&S.conv, pb * 4 * cap * nconv}, {(void **)&S.aux, pb * 4 * cap * naux},
 	             {(void **)&S.scan, pb * 4 * cap * no}, {(void **)&S.att2, pb * 4 * cap * no}, {(void **)&S.y1, pb * 4 * cap * W}, {(void **)&S.y2, pb * 4 * cap * W},
-	             {(void **)&S.hist, 4 * cap * W * (size_t)S.hist_slabs},
+	             {(void **)&S.hist, 4 * cap * W * (size_t)S.hist_slabs}, {(void **)&S.hsh, 4 * cap * shared_ff},
+	             {(void **)&S.lat16, lat16}, {(void **)&S.latkv, latkv}, {(void **)&S.lat_ek, lat_ek}, {(void **)&S.lat_ev, lat_ev},
 	             {(void **)&S.moe_gu, moe ? 4 * cap * top * 2 * ff : 0}, {(void **)&S.moe_ys, moe ? 4 * cap * top * W : 0}, {(void **)&S.order, 4 * cap * top}};
 	size_t total = 0;
 	for (auto &sl : slots) total += pad(sl.bytes);
@@ -613,7 +633,7 @@ void Model::cuda_stack(int device) {
 	cudaMemset(S.arena, 0, total);
 	char *p = S.arena;
 	for (auto &sl : slots) *sl.p = sl.bytes ? p : nullptr, p += pad(sl.bytes);
-	if (s.parallel_block)
+	if (side_bufs)
 		for (int i = 0; i < 2; ++i)
 			if (cudaStreamCreateWithFlags(&S.side[i], cudaStreamNonBlocking) != cudaSuccess ||
 			    cudaEventCreateWithFlags(&S.fork[i], cudaEventDisableTiming) != cudaSuccess ||
@@ -696,7 +716,7 @@ int Model::stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const f
 		for (int s = 0; s < ns; ++s) order[at[ids[s]]++] = s; // stable: slots of an expert stay in row order
 	}
 	ST_TRY(cudaMemcpyAsync(S.order, order.data(), sizeof(int) * ns, cudaMemcpyHostToDevice, st));
-	if (f.identity > 0) ST_TRY(yalm_moe_down_slots_real(S.y, W, S.h, L.wdown, static_cast<int>(c.weight_dtype), S.ids, S.wts, n, top, ff, W, f.weight_on_input ? 0 : 1, 0, x, W, st)); // n_real = 0: every slot as an identity slot; the real ones are overwritten below
+	if (f.identity > 0) ST_TRY(yalm_moe_identity_slots(S.y, W, x, W, S.ids, S.wts, n, top, W, E, f.weight_on_input ? 0 : 1, st));
 	if (nr == 0) return (int)cudaGetLastError();
 	ST_TRY(yalm_moe_gather_rows16(a16, x, W, S.order, S.wts, nr, top, W, bf16, f.weight_on_input ? 1 : 0, st));
 	const size_t es = dtype_size(c.weight_dtype);
@@ -860,12 +880,28 @@ int Model::stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int i
 		ST_TRY(yalm_latent_post_rows(P, ldp, L.o_q, a.q_rank, L.qnorm, L.o_kv, a.kv_rank, a.rot_dim, L.knorm, own ? L.kring : nullptr, L.ring, L.rot_freq,
 		                             L.rot_mag, a.rot.dims, a.rot.interleaved ? 1 : 0, sp.norm_eps, f32, n, pos0, ctl, st));
 		ST_TRY(stack_linear(*this, c, S.a16, S.conv, nq, P + L.o_q, ldp, L.wuq, n, nq, a.q_rank, 1.f, st));
+		const int dk = m.dim + a.rot_dim;
+		if (!f32 && !ctl && n >= 16 && m.window > 0 && m.dim > 0 && S.lat16 && a.kv_rank % 8 == 0 && nq % 4 == 0 && no % 2 == 0 && (m.heads * (m.dim + m.vdim)) % 4 == 0 &&
+		    yalm_attn_window_pool_mma_shape(dk, m.vdim) && !attn_mma_off()) {
+			// A prompt portion in 16-bit: the latents of the visible rows times [W_uk ; W_uv] on the tensor cores give every head's keys
+			// and values, written beside the rotated key part into head-major rings for the windowed tensor-core attention; the queries
+			// stay as projected, their rotated part turned in place.
+			const int first = std::max(0, pos0 - m.window + 1), count = pos0 + n - first, nkv = m.heads * (m.dim + m.vdim);
+			ST_TRY(yalm_latent_gather_rows16(S.lat16, L.kring, L.ring, row, a.kv_rank, first, count, st));
+			ST_TRY(yalm_gemm_16(S.latkv, nkv, S.lat16, L.wuk, count, nkv, a.kv_rank, 0, dt == YALM_BF16, 1.f, st));
+			ST_TRY(yalm_latent_pack_rings(S.lat_ek, S.lat_ev, S.latkv, nkv, L.kring, L.ring, a.kv_rank, a.rot_dim, m.heads, m.dim, m.vdim, L.ring, first, count, st));
+			ST_TRY(yalm_rotate_heads_rows(S.conv, nq, m.heads, dk, m.dim, L.rot_freq, L.rot_mag, a.rot.dims, a.rot.interleaved ? 1 : 0, n, pos0, ctl, st));
+			ST_TRY(yalm_attn_window_pool_mma(S.att, no, S.conv, nq, S.lat_ek, S.lat_ev, nullptr, nullptr, n, m.heads, m.heads, dk, m.vdim, L.ring, 0, m.window, 0,
+			                                 m.scale, pos0, ctl, st));
+			if (m.out_gate) ST_TRY(yalm_sigmoid_gate_rows(S.att, no, P + L.o_gate, ldp, n, no, st));
+		} else {
 		ST_TRY(yalm_latent_query_rows(S.aux, nqa, S.conv, nq, L.wuk, dt, n, m.heads, m.dim, a.rot_dim, a.kv_rank, L.rot_freq, L.rot_mag, a.rot.dims,
 		                              a.rot.interleaved ? 1 : 0, pos0, ctl, st));
 		// every head reads the one row of a position: keys are whole rows, values their first kv_rank channels
 		ST_TRY(yalm_attn_window_pool_strided(S.scan, nl, S.aux, nqa, L.kring, row, L.kring, row, nullptr, nullptr, S.attn_ws, n, m.heads, 1, row, a.kv_rank,
 		                                     L.ring, 0, m.window, 0, m.scale, f32, c.max_seq_len, pos0, ctl, st));
 		ST_TRY(yalm_head_linear_gate_rows(S.att, no, S.scan, nl, L.wuv, dt, m.out_gate ? P + L.o_gate : nullptr, ldp, n, m.heads, m.vdim, a.kv_rank, st));
+		}
 		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, no, L.wo, n, W, no, 1.f, st));
 	} else {
 		const yalm::GlaSpec &g = ls.gla;
@@ -882,8 +918,7 @@ int Model::stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int i
 	const float *add_a = S.y1, *add_b = nullptr, *slots = nullptr;
 	int nsum = 0;
 	if (f.kind != FfnSpec::None) {
-		ST_TRY(yalm_residual_sum_rows(S.x, S.y1, nullptr, nullptr, 0, 0, n, W, st));
-		ST_TRY(yalm_norm_conv_rows(S.hs, S.xn, S.x, L.norm2, sp.layer_norm ? 1 : 0, sp.norm_eps, L.inconv2, L.inconv2_state, n, W, taps, pos0, ctl, st));
+		ST_TRY(yalm_add_norm_conv_rows(S.hs, S.xn, S.x, S.y1, L.norm2, sp.layer_norm ? 1 : 0, sp.norm_eps, L.inconv2, L.inconv2_state, n, W, taps, pos0, ctl, st));
 		add_a = nullptr;
 		const int act = glu_act_code(f.act);
 		if (f.kind == FfnSpec::Dense) {
@@ -893,10 +928,19 @@ int Model::stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int i
 			add_a = S.y1;
 		} else {
 			const int EA = f.experts + f.identity;
-			if (f.shared_ff > 0) { // before the routed experts: the grouped route waits on the host for the chosen experts
-				ST_TRY(stack_linear(*this, c, S.a16, S.gu, 2 * f.shared_ff, S.hs, W, L.wsgu, n, 2 * f.shared_ff, W, 1.f, st));
-				ST_TRY(yalm_glu_act_rows(S.h, S.gu, n, f.shared_ff, glu_act_code(f.shared_act), 1.f, 0.f, 0.f, st));
-				ST_TRY(stack_linear(*this, c, S.a16, S.y2, W, S.h, f.shared_ff, L.wsdown, n, W, f.shared_ff, 1.f, st));
+			cudaStream_t ss = st;
+			if (f.shared_ff > 0) {
+				// The shared expert and the routed ones both read the same input and own their buffers: the shared expert runs on a
+				// side stream (a parallel branch of the captured decode step), enqueued first because the grouped route of a prompt
+				// portion waits on the host for the chosen experts.
+				if (!branches_off() && S.side[0]) {
+					ss = S.side[0];
+					ST_TRY(cudaEventRecord(S.fork[0], st));
+					ST_TRY(cudaStreamWaitEvent(ss, S.fork[0], 0));
+				}
+				ST_TRY(stack_linear(*this, c, ss == st ? S.a16 : S.a16e, S.gu, 2 * f.shared_ff, S.hs, W, L.wsgu, n, 2 * f.shared_ff, W, 1.f, ss));
+				ST_TRY(yalm_glu_act_rows(S.hsh, S.gu, n, f.shared_ff, glu_act_code(f.shared_act), 1.f, 0.f, 0.f, ss));
+				ST_TRY(stack_linear(*this, c, ss == st ? S.a16 : S.a16e, S.y2, W, S.hsh, f.shared_ff, L.wsdown, n, W, f.shared_ff, 1.f, ss));
 				add_b = S.y2;
 			}
 			ST_TRY(yalm_router_bias_topk_rows(S.ids, S.wts, S.hs, W, L.router, dt, n, EA, f.top, W, f.score == yalm::RouterScore::Sigmoid ? 1 : 0,
@@ -910,6 +954,10 @@ int Model::stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int i
 				ST_TRY(yalm_moe_down_slots_real(S.y, W, S.h, L.wdown, dt, S.ids, S.wts, n, f.top, f.ff, W, f.weight_on_input ? 0 : 1, f.experts, S.hs, W, st));
 			}
 			slots = S.y, nsum = f.top;
+			if (ss != st) {
+				ST_TRY(cudaEventRecord(S.join[0], ss));
+				ST_TRY(cudaStreamWaitEvent(st, S.join[0], 0));
+			}
 		}
 	}
 	// the layer's result (x + what is still to be added) joins the earlier ones; x becomes their weighted sum

@@ -59,6 +59,40 @@ __device__ __forceinline__ int first_pos(const int *ctl, int pos0) { return ctl 
 
 __host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// dot(weight row, x) over K elements, result in every lane.  `vec`: the row and x are 16-byte aligned and K % VEC == 0.
+template <int DT>
+__device__ __forceinline__ float warp_dot(const void *w, size_t row_off, const float *__restrict__ x, int K, bool vec) {
+	using E = Elem<DT>;
+	const int lane = threadIdx.x & 31;
+	float acc = 0.f;
+	if (vec) {
+		const typename E::T *row = static_cast<const typename E::T *>(w) + row_off;
+		constexpr int U = 4, STEP = 32 * E::VEC; // U loads in flight per lane before the first multiply
+		for (int k0 = lane * E::VEC; k0 < K; k0 += U * STEP) {
+			uint4 wv[U];
+#pragma unroll
+			for (int u = 0; u < U; ++u)
+				if (k0 + u * STEP < K) wv[u] = ldg_stream(row + k0 + u * STEP);
+#pragma unroll
+			for (int u = 0; u < U; ++u)
+				if (k0 + u * STEP < K) {
+					float f[8];
+					E::unpack(wv[u], f);
+					const int k = k0 + u * STEP;
+#pragma unroll
+					for (int i = 0; i < E::VEC; i += 4) {
+						const float4 xv = *reinterpret_cast<const float4 *>(x + k + i);
+						acc = fmaf(f[i], xv.x, acc), acc = fmaf(f[i + 1], xv.y, acc), acc = fmaf(f[i + 2], xv.z, acc), acc = fmaf(f[i + 3], xv.w, acc);
+					}
+				}
+		}
+	} else {
+		for (int k = lane; k < K; k += 32) acc = fmaf(E::get(w, row_off + k), x[k], acc);
+	}
+	return warp_sum(acc);
+}
+
+
 __device__ __forceinline__ float glu_value(float g, float u, int act, float alpha, float limit, float up_offset) {
 	if (limit > 0.f) g = fminf(g, limit), u = fminf(fmaxf(u, -limit), limit);
 	float a;

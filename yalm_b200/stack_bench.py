@@ -251,6 +251,174 @@ def run_fapudra(args, base, emit, shm_path, ClockSampler):
                           l2="inputs larger than L2 (weights streamed per token)")))
 
 
+# ---- Fegizen ---------------------------------------------------------------------------------------------------------------
+# name: width; latent attention heads x (dim unrotated + rot rotated) keys, vdim values, latent sizes, window; linear attention
+# heads x (dim, vdim) and the decay's low-rank size; experts (+ identity experts, shared expert); layer order (l = latent
+# attention with experts, s = latent attention reading the first layer's cache, g = linear attention)
+FEGIZEN_SIZES = {
+    "w1024": dict(width=1024, heads=8, dim=64, rot=64, vdim=128, kv_rank=256, q_rank=512, window=1024, gheads=8, gdim=128, gvdim=128, rank=64,
+                  moe_ff=1024, experts=8, identity=2, top=2, shared=1024, order="lggs", vocab=32000),
+    "w2048": dict(width=2048, heads=16, dim=64, rot=64, vdim=128, kv_rank=512, q_rank=1024, window=1024, gheads=16, gdim=128, gvdim=128, rank=64,
+                  moe_ff=2048, experts=8, identity=2, top=2, shared=2048, order="lggs", vocab=32000),
+}
+
+
+def write_fegizen(folder, z):
+    """A checkpoint directory of the given size: matrices tiled from one random block, norm weights 1, depth weights 1 on the
+    newest result."""
+    os.makedirs(folder, exist_ok=True)
+    rng = np.random.default_rng(3)
+    block = _bf16(rng.standard_normal(1 << 22).astype(np.float32) * 0.02)
+    W, taps = z["width"], 4
+    mlp = {"kind": "moe", "expert": {"ff": z["moe_ff"]}, "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 1.0},
+           "shared": {"ff": z["shared"]}}
+    rot = {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    lat = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
+           "mask": {"size": z["window"]}, "rot": rot, "scale": (z["dim"] + z["rot"]) ** -0.5}
+    gla = {"heads": z["gheads"], "dim": z["gdim"], "vdim": z["gvdim"], "tau": 16.0}
+    layers = [{"type": "latent_attention", "mixer": lat, "mlp": mlp} if c == "l" else
+              {"type": "latent_attention", "mixer": dict(lat, kv_from=z["order"].index("l")), "mlp": mlp} if c == "s" else
+              {"type": "gla", "mixer": gla, "mlp": mlp} for c in z["order"]]
+    cfg = {"architecture": "Fegizen", "width": W, "vocab": z["vocab"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0}, "canon": {"taps": taps},
+           "logit_scale": 1.0, "layers": layers}
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    shapes = {"embed": (z["vocab"], W), "final.norm": (W,), "head": (z["vocab"], W)}
+    EA = z["experts"] + z["identity"]
+    for i, c in enumerate(z["order"]):
+        p, m, f = "l%d." % i, "l%d.mix." % i, "l%d.mlp." % i
+        shapes.update({p + "norm1": (W,), p + "norm2": (W,), p + "canon1": (W, taps), p + "canon2": (W, taps), p + "dwa": (i + 2,),
+                       f + "router": (EA, W), f + "correction": (EA,), f + "shared.gate": (z["shared"], W), f + "shared.up": (z["shared"], W),
+                       f + "shared.down": (W, z["shared"])})
+        for e in range(z["experts"]):
+            shapes.update({f + "e%d.gate" % e: (z["moe_ff"], W), f + "e%d.up" % e: (z["moe_ff"], W), f + "e%d.down" % e: (W, z["moe_ff"])})
+        if c in "ls":
+            H, no = z["heads"], z["heads"] * z["vdim"]
+            shapes.update({m + "dq": (z["q_rank"], W), m + "dq.norm": (z["q_rank"],), m + "uq": (H * (z["dim"] + z["rot"]), z["q_rank"]),
+                           m + "uk": (H * z["dim"], z["kv_rank"]), m + "uv": (no, z["kv_rank"]), m + "g": (no, W), m + "o": (W, no)})
+            if c == "l":
+                shapes.update({m + "dkv": (z["kv_rank"] + z["rot"], W), m + "dkv.norm": (z["kv_rank"],)})
+        else:
+            hd, hp = z["gheads"] * z["gdim"], z["gheads"] * z["gvdim"]
+            shapes.update({m + "q": (hd, W), m + "k": (hd, W), m + "v": (hp, W), m + "g": (hp, W), m + "o": (W, hp), m + "norm": (z["gvdim"],),
+                           m + "a1": (z["rank"], W), m + "a2": (hd, z["rank"]), m + "a2.b": (hd,)})
+    header, off = {}, 0
+    for name, shp in shapes.items():
+        n = int(np.prod(shp))
+        header[name] = {"dtype": "BF16", "shape": list(shp), "data_offsets": [off, off + 2 * n]}
+        off += 2 * n
+    h = json.dumps(header).encode()
+    h += b" " * (-len(h) % 8)
+    one, zero = _bf16(np.ones(1, np.float32))[0], np.uint16(0)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h)
+        for k, (name, shp) in enumerate(shapes.items()):
+            n = int(np.prod(shp))
+            if name.endswith("norm") or name.endswith("norm1") or name.endswith("norm2"):
+                f.write(np.full(n, one, np.uint16).tobytes())
+            elif name.endswith(".dwa"):
+                f.write(np.array([zero] * (n - 1) + [one], np.uint16).tobytes())
+            elif len(shp) < 2:
+                f.write(block[:n].tobytes())
+            else:
+                f.write(np.resize(np.roll(block, 7919 * k), n).tobytes())
+    return cfg
+
+
+def fegizen_numbers(z):
+    """-> (decode bytes per token at CONTEXT, prefill FLOP per token): the active matrices once (bf16), the fp32 matrix states read
+    and written, the window of cached rows (one row per position for all heads); 2 FLOP per active parameter plus the attention's
+    and the recurrence's own products (queries against the cached rows: heads x (kv_rank + rot) per key, twice)."""
+    W = z["width"]
+    experts = z["top"] * 3 * z["moe_ff"] * W + (z["experts"] + z["identity"]) * W + 3 * z["shared"] * W
+    params, state, extra = z["vocab"] * W, 0, 0.0
+    seen = min(CONTEXT, z["window"])
+    for c in z["order"]:
+        if c in "ls":
+            H, no, row = z["heads"], z["heads"] * z["vdim"], z["kv_rank"] + z["rot"]
+            params += (z["q_rank"] + (row if c == "l" else 0) + 2 * no) * W + H * (z["dim"] + z["rot"]) * z["q_rank"] + H * z["dim"] * z["kv_rank"] + \
+                no * z["kv_rank"] + experts
+            state += seen * row * 2
+            extra += 2.0 * H * seen * (row + z["kv_rank"])
+        else:
+            hd, hp = z["gheads"] * z["gdim"], z["gheads"] * z["gvdim"]
+            params += (2 * hd + 2 * hp + z["rank"]) * W + z["rank"] * hd + hp * W + experts
+            state += 2 * 4 * z["gheads"] * z["gdim"] * z["gvdim"]
+            extra += 6.0 * z["gheads"] * z["gdim"] * z["gvdim"]
+    return 2 * params + state, 2.0 * (params - z["vocab"] * W) + extra
+
+
+def run_fegizen(args, base, emit, shm_path, ClockSampler):
+    """`bench.py --workload fegizen-sizes`: the Fegizen design beside the closest existing model on the same executor, Fapudra
+    (windowed attention + a matrix-state recurrence + routed experts), at equal width, heads, window, experts, layers and
+    vocabulary."""
+    import torch
+    from yalm_b200 import api
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = json.load(open(pk)) if os.path.exists(pk) else {"hbm_gbs": 6650.0, "bf16_tflops_sustained": 1400.0}
+    hbm, tflops = float(peaks["hbm_gbs"]), float(peaks["bf16_tflops_sustained"])
+    steps = max(8, min(args.steps, 128))
+    clocks = ClockSampler(0)
+    clocks.start()
+    out, launches = [], 0
+
+    def measure(model, ids):
+        st = api.InferenceState(model)
+        st.forward_batch(ids[:1024], 0)                     # warm-up (sizes kernels, first-use set-up)
+        st.end_sequence()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        st.forward_batch(ids[:-1], 0)
+        t_pre = time.perf_counter() - t0
+        st.generate_greedy(ids[-1], CONTEXT - 1, max(3, args.warmup))   # first step eager + graph capture, untimed
+        st.generate_greedy(ids[0], CONTEXT - 1 + max(3, args.warmup), steps)
+        t_dec = st.device_ms / 1e3
+        n = model.launches()
+        st.close()
+        return (CONTEXT - 1) / t_pre, steps / t_dec, n
+
+    only = os.environ.get("YALM_BENCH_SIZES", "").split(",") if os.environ.get("YALM_BENCH_SIZES") else None
+    for name, z in FEGIZEN_SIZES.items():
+        if only and name not in only:
+            continue
+        ids = [(i * 7919 + 1) % z["vocab"] for i in range(CONTEXT)]
+        row = {"size": name, "width": z["width"], "layers": z["order"], "context": CONTEXT, "window": z["window"]}
+        folder = shm_path("yalm_bench_fegizen_%s_%d" % (name, os.getpid()))
+        try:
+            write_fegizen(folder, z)
+            model = api.Model(folder, CONTEXT + steps + args.warmup + 8, api.BF16).cuda(0)
+        finally:
+            shutil.rmtree(folder, ignore_errors=True)
+        pre, dec, n = measure(model, ids)
+        model.close()
+        dec_bytes, pre_flop = fegizen_numbers(z)
+        launches += steps * n
+        row["fegizen"] = {"prefill_tok_s": pre, "decode_tok_s": dec, "prefill_frac_of_measured_bf16": pre_flop * pre / 1e12 / tflops,
+                          "decode_frac_of_measured_hbm": dec_bytes * dec / 1e9 / hbm, "decode_bytes_per_token": dec_bytes, "launches_per_token": n}
+        if not os.environ.get("YALM_BENCH_NO_PEER"):
+            zf = dict(FAPUDRA_SIZES[name])
+            folder = shm_path("yalm_bench_fapudra_%s_%d" % (name, os.getpid()))
+            try:
+                write_fapudra(folder, zf, CONTEXT + steps + args.warmup + 8)
+                model = api.Model(folder, 0, api.BF16).cuda(0)
+            finally:
+                shutil.rmtree(folder, ignore_errors=True)
+            pre, dec, n = measure(model, ids)
+            model.close()
+            f_bytes, f_flop = fapudra_numbers(zf)
+            row["equal_size_fapudra"] = {"prefill_tok_s": pre, "decode_tok_s": dec, "prefill_frac_of_measured_bf16": f_flop * pre / 1e12 / tflops,
+                                         "decode_frac_of_measured_hbm": f_bytes * dec / 1e9 / hbm, "decode_bytes_per_token": f_bytes, "launches_per_token": n}
+        out.append(row)
+    clk = clocks.stop()
+    first = out[0]["fegizen"]
+    emit(dict(base, impl="ours", metric="batch-1 decode tok/s (Fegizen, first size; all sizes under `sizes`)", value=first["decode_tok_s"], steps=steps,
+              ms_per_step=1000.0 / first["decode_tok_s"], dtype="bf16", clocks=clk, gpu_launches=launches, sizes=out,
+              e2e={"value": first["decode_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
+                   "note": "device loop: token ids stay on the device, 4 bytes per token come back"},
+              config=dict(base["config"], workload="Fegizen at model-like sizes beside the equal-size Fapudra stack", context=CONTEXT,
+                          l2="inputs larger than L2 (weights streamed per token)")))
+
+
 def run(args, base, emit, write_yalm, shm_path, ClockSampler):
     import torch
     from yalm_b200 import api
