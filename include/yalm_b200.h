@@ -342,6 +342,12 @@ int yalm_rotate_heads_rows(float *q, int ldq, int heads, int head_size, int offs
                            int interleaved, int n, int pos0, const int *ctl, yalm_stream_t s);
 /* x[m, :dim] *= sigmoid(gate[m, :dim]) */
 int yalm_sigmoid_gate_rows(float *x, int ldx, const float *gate, int ldg, int n, int dim, yalm_stream_t s);
+/* Attention over cached bf16 rows that all heads share (key = the row's dk channels, value = its first dv; row stride ld), each
+ * row read once for scores and weighted sums: position i sees rows j with 0 <= i - j < window (0: all).  Sizes:
+ * yalm_attn_latent_rows_shape; workspace as for yalm_attn_window_pool (or NULL). */
+int yalm_attn_latent_rows_shape(int dk, int dv, int ld);
+int yalm_attn_latent_rows(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *workspace, int n, int n_heads, int dk,
+                          int dv, int ring, int window, float scale, int context, int pos0, const int *ctl, yalm_stream_t s);
 /* out[m, h, :N] = w_h x[m, h, :K] (w (heads N, K)), times sigmoid(gate[m, h, :N]) if gate. */
 int yalm_head_linear_gate_rows(float *out, int ldo, const float *x, int ldx, const void *w, int dtype, const float *gate, int ldg, int n, int heads,
                                int N, int K, yalm_stream_t s);

@@ -223,6 +223,54 @@ def test_attention_edges_of_the_window(dk, dv, H, sizes):
         assert np.abs(got[i, i % H] - rows[target[i], :dv]).max() > 0.05
 
 
+def run_attention_one_pass(q, rows, dv, window, scale, ring, sizes):
+    """The kernel that reads every bf16 row once for scores and sums."""
+    L = api.lib()
+    L.yalm_attn_latent_rows.argtypes = [vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, i32, i32, i32, f32, i32, i32, vp, vp]
+    L.yalm_attn_window_pool_workspace.restype = sz
+    L.yalm_attn_window_pool_workspace.argtypes = [i32]
+    T, H, dk = q.shape
+    ws = torch.zeros(L.yalm_attn_window_pool_workspace(dv), device="cuda")
+    qd = dev(q.reshape(T, -1))
+    ringbuf = torch.full((ring, dk), 50.0, device="cuda", dtype=torch.bfloat16)
+    rd = dev(rows, torch.bfloat16)
+    out = torch.zeros(T, H * dv, device="cuda")
+    for at, n in portions(T, sizes):
+        for t in range(at, at + n):
+            ringbuf[t % ring] = rd[t]
+        ok(L.yalm_attn_latent_rows(ptr(out[at:]), H * dv, ptr(qd[at:]), H * dk, ptr(ringbuf), dk, ptr(ws), n, H, dk, dv, ring, window, scale, 4096, at, None, None),
+           "attn_latent_rows")
+    return out.cpu().numpy().reshape(T, H, dv)
+
+
+@pytest.mark.parametrize("dk,dv,H", [(24, 16, 3), (160, 128, 8), (320, 256, 2), (576, 512, 5), (72, 57, 1)])
+@pytest.mark.parametrize("sizes", [[1000], [1], [2, 1, 30]])
+def test_one_pass_attention_edges_of_the_window(dk, dv, H, sizes):
+    """The same crafted queries through the kernel that serves bf16 caches; rows are bf16 values, so the comparison is exact
+    up to fp32 summation order."""
+    rng = np.random.default_rng(dk)
+    T, window = 90, 17
+    rows = rng.standard_normal((T, dk))
+    rows = O.bf16_round(rows / np.linalg.norm(rows, axis=-1, keepdims=True)).astype(np.float64)
+    q = rng.standard_normal((T, H, dk)) * 0.1
+    target = {}
+    for i in range(T):
+        j = [i - window + 1, i - window, 0, i][i % 4]
+        if 0 <= j <= i:
+            q[i, i % H] = 40.0 * rows[j]
+            target[i] = j
+    want = attend(q, rows, dv, window, 1.0)
+    got = run_attention_one_pass(q, rows, dv, window, 1.0, window + max(min(s, T) for s in sizes), sizes)
+    close_enough(got, want, 2e-5)
+    for other in (window - 1, window + 1):
+        assert np.abs(attend(q, rows, dv, other, 1.0) - want).max() > 0.05
+    for i, j in target.items():
+        if i - j == window - 1 and i % 4 == 0:
+            np.testing.assert_allclose(got[i, i % H], rows[j, :dv], atol=3e-3)
+        if i - j == window:
+            assert np.abs(got[i, i % H] - rows[j, :dv]).max() > 0.05
+
+
 def test_attention_far_key_without_a_window_and_bf16_rows():
     rng = np.random.default_rng(2)
     T, H, dk, dv = 700, 4, 40, 32
@@ -236,6 +284,9 @@ def test_attention_far_key_without_a_window_and_bf16_rows():
         got = run_attention(q, rows, dv, 0, 1.0, T, [650, 1], cache_f32=f32c)
         close_enough(got, want, 2e-5)
         np.testing.assert_allclose(got[T - 1, 1], rows[3, :dv], atol=2e-3)
+    got = run_attention_one_pass(q, rows, dv, 0, 1.0, T, [650, 1])
+    close_enough(got, want, 2e-5)
+    np.testing.assert_allclose(got[T - 1, 1], rows[3, :dv], atol=2e-3)
 
 
 # ---- gated linear attention: the recurrence -----------------------------------------------------------------------------------------

@@ -41,7 +41,7 @@ SYMBOLS = [
     "yalm_head_norm_gate_rows", "yalm_qk_bias_append_rows", "yalm_attn_sigmoid_rows", "yalm_attn_sigmoid_workspace", "yalm_gemv_norm_shift", "yalm_gemv_residual_sum", "yalm_attn_sigmoid_mma", "yalm_attn_sigmoid_mma_shape", "yalm_residual_sum_rows", "yalm_softcap_rows", "yalm_attn_window_pool_host", "yalm_gemv_scaled", "yalm_gemv_norm_residual", "yalm_gemv_qkv_post", "yalm_attn_window_pool_mma", "yalm_attn_window_pool_mma_shape", "yalm_attn_window_pool_workspace",
     "yalm_norm_conv_rows", "yalm_latent_post_rows", "yalm_latent_query_rows", "yalm_head_linear_gate_rows", "yalm_gla_prep_rows", "yalm_depth_average_rows",
     "yalm_layer_norm_gather_rows", "yalm_head_norm_act_rows", "yalm_attn_window_pool_strided", "yalm_router_bias_topk_rows", "yalm_moe_glu_slots_real",
-    "yalm_moe_down_slots_real", "yalm_add_norm_conv_rows", "yalm_moe_identity_slots", "yalm_latent_gather_rows16", "yalm_latent_pack_rings", "yalm_rotate_heads_rows", "yalm_sigmoid_gate_rows",
+    "yalm_moe_down_slots_real", "yalm_attn_latent_rows", "yalm_attn_latent_rows_shape", "yalm_add_norm_conv_rows", "yalm_moe_identity_slots", "yalm_latent_gather_rows16", "yalm_latent_pack_rings", "yalm_rotate_heads_rows", "yalm_sigmoid_gate_rows",
     "yalm_tp_unique_id", "yalm_tp_init", "yalm_tp_finalize", "yalm_tp_shard_plan", "yalm_mega_tile_plan", "yalm_mega_attn_split", "yalm_mega_mma_plan", "yalm_mega_hb_share", "yalm_error_string", "yalm_version",
 ]
 

@@ -321,6 +321,159 @@ __global__ void sigmoid_gate_rows_kernel(float *__restrict__ x, int ldx, const f
 	if (e < dim) x[(size_t)m * ldx + e] /= 1.0f + expf(-gate[(size_t)m * ldg + e]);
 }
 
+// ---- latent attention over cached rows, one pass ---------------------------------------------------------------------------------
+// Every head reads the same bf16 row [latent | rotated key part] of a position: its key is the whole row (dk channels), its
+// value the row's first dv channels.  A warp takes one row at a time as 16-byte pieces (lane l holds pieces l, l + 32, ...: one
+// instruction fetches 512 contiguous bytes), so a row is read ONCE for the scores of R heads and for their weighted sums: the
+// pieces that made the score are the value.  KB rows are in flight per warp; their scores are reduced with shuffles, one
+// online-softmax correction is applied per batch, and the warps of a CTA and the splits of a query merge as in the windowed
+// attention (partials: accumulator, max, sum).  grid (head groups, rows, splits).
+constexpr int kLaWarps = 4, kLaBatch = 4, kLaMaxParts = 4096;
+template <int R, int NP>
+__global__ void __launch_bounds__(kLaWarps * 32) attn_latent_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+                                                                         const __nv_bfloat16 *__restrict__ rows, int ld, float *__restrict__ part,
+                                                                         int n_heads, int dk, int dv, int ring, int window, float scale, int pos0,
+                                                                         const int *__restrict__ ctl) {
+	extern __shared__ __align__(16) float sm[];
+	const int dkp = NP * 256;
+	float *qs = sm;                               // R x dkp, zero beyond dk
+	float *macc = qs + R * dkp;                   // kLaWarps x R x dv
+	float *mml = macc + kLaWarps * R * dv;        // kLaWarps x R x 2
+	const int h0 = blockIdx.x * R, nh = min(R, n_heads - h0), m = blockIdx.y, z = blockIdx.z, nsplit = gridDim.z;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int i = first_pos(ctl, pos0) + m, lo = window > 0 ? max(0, i - window + 1) : 0, ntok = i - lo + 1;
+	for (int e = threadIdx.x; e < R * dkp; e += blockDim.x) {
+		const int r = e / dkp, d = e % dkp;
+		qs[e] = (r < nh && d < dk) ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
+	}
+	__syncthreads();
+	float mx[R], l[R], acc[R][NP][8];
+#pragma unroll
+	for (int r = 0; r < R; ++r) {
+		mx[r] = -INFINITY, l[r] = 0.f;
+#pragma unroll
+		for (int p = 0; p < NP; ++p)
+#pragma unroll
+			for (int j = 0; j < 8; ++j) acc[r][p][j] = 0.f;
+	}
+	const int per = (ntok + nsplit - 1) / nsplit, k_end = min(ntok, (z + 1) * per);
+	for (int k0 = z * per + warp * kLaBatch; k0 < k_end; k0 += kLaWarps * kLaBatch) {
+		uint4 w[kLaBatch][NP];
+#pragma unroll
+		for (int b = 0; b < kLaBatch; ++b) {
+			const __nv_bfloat16 *row = rows + (size_t)((lo + min(k0 + b, k_end - 1)) % ring) * ld; // past the end: a repeated row with no weight
+#pragma unroll
+			for (int p = 0; p < NP; ++p) {
+				const int c = (lane + 32 * p) * 8;
+				w[b][p] = c < dk ? __ldg(reinterpret_cast<const uint4 *>(row + c)) : make_uint4(0, 0, 0, 0);
+			}
+		}
+		float d[kLaBatch][R];
+#pragma unroll
+		for (int b = 0; b < kLaBatch; ++b) {
+#pragma unroll
+			for (int r = 0; r < R; ++r) d[b][r] = 0.f;
+#pragma unroll
+			for (int p = 0; p < NP; ++p) {
+				float f[8];
+				Elem<YALM_BF16>::unpack(w[b][p], f);
+#pragma unroll
+				for (int r = 0; r < R; ++r) {
+					const float4 q0 = *reinterpret_cast<const float4 *>(qs + r * dkp + (lane + 32 * p) * 8), q1 = *reinterpret_cast<const float4 *>(qs + r * dkp + (lane + 32 * p) * 8 + 4);
+					d[b][r] = fmaf(f[0], q0.x, d[b][r]), d[b][r] = fmaf(f[1], q0.y, d[b][r]), d[b][r] = fmaf(f[2], q0.z, d[b][r]), d[b][r] = fmaf(f[3], q0.w, d[b][r]);
+					d[b][r] = fmaf(f[4], q1.x, d[b][r]), d[b][r] = fmaf(f[5], q1.y, d[b][r]), d[b][r] = fmaf(f[6], q1.z, d[b][r]), d[b][r] = fmaf(f[7], q1.w, d[b][r]);
+				}
+			}
+		}
+#pragma unroll
+		for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+			for (int b = 0; b < kLaBatch; ++b)
+#pragma unroll
+				for (int r = 0; r < R; ++r) d[b][r] += __shfl_xor_sync(kFull, d[b][r], o);
+		float pw[kLaBatch][R];
+#pragma unroll
+		for (int r = 0; r < R; ++r) {
+			float nm = mx[r];
+#pragma unroll
+			for (int b = 0; b < kLaBatch; ++b)
+				if (k0 + b < k_end) nm = fmaxf(nm, d[b][r]);
+			const float corr = mx[r] == -INFINITY ? 0.f : expf(mx[r] - nm);
+			float ps = 0.f;
+#pragma unroll
+			for (int b = 0; b < kLaBatch; ++b) pw[b][r] = k0 + b < k_end ? expf(d[b][r] - nm) : 0.f, ps += pw[b][r];
+			l[r] = l[r] * corr + ps, mx[r] = nm;
+#pragma unroll
+			for (int p = 0; p < NP; ++p)
+#pragma unroll
+				for (int j = 0; j < 8; ++j) acc[r][p][j] *= corr;
+		}
+#pragma unroll
+		for (int b = 0; b < kLaBatch; ++b)
+#pragma unroll
+			for (int p = 0; p < NP; ++p) {
+				float f[8];
+				Elem<YALM_BF16>::unpack(w[b][p], f);
+#pragma unroll
+				for (int r = 0; r < R; ++r)
+#pragma unroll
+					for (int j = 0; j < 8; ++j) acc[r][p][j] = fmaf(pw[b][r], f[j], acc[r][p][j]);
+			}
+	}
+#pragma unroll
+	for (int r = 0; r < R; ++r) {
+#pragma unroll
+		for (int p = 0; p < NP; ++p)
+#pragma unroll
+			for (int j = 0; j < 8; ++j) {
+				const int c = (lane + 32 * p) * 8 + j;
+				if (c < dv) macc[(warp * R + r) * dv + c] = acc[r][p][j];
+			}
+		if (lane == 0) mml[(warp * R + r) * 2] = mx[r], mml[(warp * R + r) * 2 + 1] = l[r];
+	}
+	__syncthreads();
+	for (int r = warp; r < nh; r += kLaWarps) { // one warp finishes one head
+		float M = -INFINITY;
+		for (int w2 = 0; w2 < kLaWarps; ++w2) M = fmaxf(M, mml[(w2 * R + r) * 2]);
+		float wt[kLaWarps], L = 0.f;
+		for (int w2 = 0; w2 < kLaWarps; ++w2) {
+			const float mw = mml[(w2 * R + r) * 2];
+			wt[w2] = mw == -INFINITY ? 0.f : expf(mw - M);
+			L += wt[w2] * mml[(w2 * R + r) * 2 + 1];
+		}
+		const int h = h0 + r;
+		float *pr = part ? part + ((size_t)(m * n_heads + h) * nsplit + z) * (dv + 2) : nullptr;
+		for (int c = lane; c < dv; c += 32) {
+			float o = 0.f;
+			for (int w2 = 0; w2 < kLaWarps; ++w2) o += wt[w2] * macc[(w2 * R + r) * dv + c];
+			if (pr) pr[c] = o;
+			else out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+		}
+		if (pr && lane == 0) pr[dv] = M, pr[dv + 1] = L;
+	}
+}
+// out[m, h, :] = sum_z w_z acc_z / sum_z w_z L_z with w_z = exp(M_z - max M), splits taken in order (a split without keys has
+// M = -inf and no weight).  grid (heads, rows).
+__global__ void attn_latent_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, int n_heads, int dv, int nsplit) {
+	const int h = blockIdx.x, m = blockIdx.y;
+	const float *pr = part + (size_t)(m * n_heads + h) * nsplit * (dv + 2);
+	float M = -INFINITY;
+	for (int z = 0; z < nsplit; ++z) M = fmaxf(M, pr[(size_t)z * (dv + 2) + dv]);
+	float L = 0.f;
+	for (int z = 0; z < nsplit; ++z) {
+		const float mz = pr[(size_t)z * (dv + 2) + dv];
+		if (mz != -INFINITY) L += expf(mz - M) * pr[(size_t)z * (dv + 2) + dv + 1];
+	}
+	for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+		float o = 0.f;
+		for (int z = 0; z < nsplit; ++z) {
+			const float mz = pr[(size_t)z * (dv + 2) + dv];
+			if (mz != -INFINITY) o += expf(mz - M) * pr[(size_t)z * (dv + 2) + c];
+		}
+		out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+	}
+}
+
 // out[r] = layer norm (or RMS norm) of x[rows[r]] times w   (rows null: r itself)
 __global__ void __launch_bounds__(256) layer_norm_gather_rows_kernel(float *__restrict__ out, const float *__restrict__ x, const int *__restrict__ rows,
                                                                      const float *__restrict__ w, int layer_norm, float eps, int dim) {
@@ -471,4 +624,44 @@ extern "C" int yalm_sigmoid_gate_rows(float *x, int ldx, const float *gate, int 
 	if (!x || !gate || n < 1 || dim < 1) return YALM_EINVAL;
 	sigmoid_gate_rows_kernel<<<dim3((dim + 255) / 256, n), 256, 0, (cudaStream_t)s>>>(x, ldx, gate, ldg, dim);
 	return (int)cudaGetLastError();
+}
+
+// 1 when yalm_attn_latent_rows has a kernel for these sizes (bf16 rows of 16-byte pieces, at most 768 channels).
+extern "C" int yalm_attn_latent_rows_shape(int dk, int dv, int ld) {
+	return dk >= 8 && dk <= 768 && dk % 8 == 0 && dv >= 1 && dv <= dk && ld >= dk && ld % 8 == 0;
+}
+
+template <int R, int NP>
+static int launch_attn_latent(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *ws, int n, int n_heads, int dk, int dv, int ring,
+                              int window, float scale, int nsplit, int pos0, const int *ctl, cudaStream_t st) {
+	const size_t smem = sizeof(float) * ((size_t)R * NP * 256 + (size_t)kLaWarps * R * dv + kLaWarps * R * 2);
+	if (smem > 96 * 1024) return YALM_EINVAL;
+	if (smem > 48 * 1024) YALM_TRY(cudaFuncSetAttribute(attn_latent_rows_kernel<R, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	attn_latent_rows_kernel<R, NP><<<dim3((n_heads + R - 1) / R, n, nsplit), kLaWarps * 32, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)rows, ld,
+	                                                                                                  nsplit > 1 ? ws : nullptr, n_heads, dk, dv, ring,
+	                                                                                                  window, scale, pos0, ctl);
+	if (nsplit > 1) attn_latent_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit);
+	return (int)cudaGetLastError();
+}
+
+// Attention of n query rows (n_heads x dk each) over cached bf16 rows shared by all heads: key = the row's dk channels, value =
+// its first dv; position i sees rows j with 0 <= i - j < window (0: all).  workspace: yalm_attn_window_pool_workspace(dv) floats
+// (split partials of calls with few rows), or null.
+extern "C" int yalm_attn_latent_rows(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *workspace, int n, int n_heads, int dk,
+                                     int dv, int ring, int window, float scale, int context, int pos0, const int *ctl, yalm_stream_t s) {
+	if (!out || !q || !rows || n < 1 || n_heads < 1 || ring < 1 || !yalm_attn_latent_rows_shape(dk, dv, ld) || ((uintptr_t)rows & 15)) return YALM_EINVAL;
+	const int R = n_heads >= 4 ? 4 : n_heads >= 2 ? 2 : 1, hg = (n_heads + R - 1) / R, NP = (dk / 8 + 31) / 32;
+	int nsplit = 1;
+	const int ctas = hg * n;
+	if (workspace && ctas < 296) { // few rows: split the keys so that every SM has work; the count depends on shapes only
+		const int most = window > 0 ? window : (context > 0 ? context : ring);
+		const int batches = (most + kLaWarps * kLaBatch - 1) / (kLaWarps * kLaBatch);
+		nsplit = std::max(1, std::min({(296 + ctas - 1) / ctas, batches, kLaMaxParts / (n * n_heads), 64}));
+	}
+	cudaStream_t st = (cudaStream_t)s;
+#define LA_CASE(R_, NP_)                                                                                                              \
+	if (R == R_ && NP == NP_) return launch_attn_latent<R_, NP_>(out, ldo, q, ldq, rows, ld, workspace, n, n_heads, dk, dv, ring, window, scale, nsplit, pos0, ctl, st)
+	LA_CASE(4, 1); LA_CASE(4, 2); LA_CASE(4, 3); LA_CASE(2, 1); LA_CASE(2, 2); LA_CASE(2, 3); LA_CASE(1, 1); LA_CASE(1, 2); LA_CASE(1, 3);
+#undef LA_CASE
+	return YALM_EINVAL;
 }

@@ -898,6 +898,11 @@ int Model::stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int i
 		ST_TRY(yalm_latent_query_rows(S.aux, nqa, S.conv, nq, L.wuk, dt, n, m.heads, m.dim, a.rot_dim, a.kv_rank, L.rot_freq, L.rot_mag, a.rot.dims,
 		                              a.rot.interleaved ? 1 : 0, pos0, ctl, st));
 		// every head reads the one row of a position: keys are whole rows, values their first kv_rank channels
+		static const bool one_pass_off = [] { const char *e = getenv("YALM_STACK_ATTN_LANES"); return e && e[0] == '0'; }();
+		if (!f32 && !one_pass_off && yalm_attn_latent_rows_shape(row, a.kv_rank, row) && ((uintptr_t)L.kring & 15) == 0 && nqa % 4 == 0)
+			ST_TRY(yalm_attn_latent_rows(S.scan, nl, S.aux, nqa, L.kring, row, S.attn_ws, n, m.heads, row, a.kv_rank, L.ring, m.window, m.scale, c.max_seq_len, pos0,
+			                             ctl, st));
+		else
 		ST_TRY(yalm_attn_window_pool_strided(S.scan, nl, S.aux, nqa, L.kring, row, L.kring, row, nullptr, nullptr, S.attn_ws, n, m.heads, 1, row, a.kv_rank,
 		                                     L.ring, 0, m.window, 0, m.scale, f32, c.max_seq_len, pos0, ctl, st));
 		ST_TRY(yalm_head_linear_gate_rows(S.att, no, S.scan, nl, L.wuv, dt, m.out_gate ? P + L.o_gate : nullptr, ldp, n, m.heads, m.vdim, a.kv_rank, st));
