@@ -27,47 +27,56 @@ namespace stack {
 
 // ---- norm + input convolution -------------------------------------------------------------------------------------------
 // Row `row` of the call (negative: a position before the call, read from the state; before the sequence: zero) normed into
-// dst (dim floats of shared memory).  Two passes for the layer norm: mean, then the mean of the squared deviations.
-__device__ __forceinline__ void normed_row(float *dst, const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ state, int row,
-                                           int p0, int taps, int dim, int layer_norm, float eps, float *red) {
+// dst (dim floats of shared memory).  Two passes for the layer norm: mean, then the mean of the squared deviations.  The row
+// goes to shared memory first, with its loads unrolled so that several are in flight per thread: with one CTA per row (and one
+// row per decode step) the memory latency of every dependent pass is the kernel's time.
+__device__ __forceinline__ void normed_row(float *dst, const float *x, const float *__restrict__ w, const float *state, int row, int p0, int taps, int dim,
+                                           int layer_norm, float eps, float *red) {
 	if (row < 0) {
 		const bool have = p0 + row >= 0;
-		for (int e = threadIdx.x; e < dim; e += blockDim.x) dst[e] = have ? state[(size_t)(taps - 1 + row) * dim + e] : 0.f;
+		const float *src = state + (size_t)(taps - 1 + row) * dim;
+#pragma unroll 8
+		for (int e = threadIdx.x; e < dim; e += blockDim.x) dst[e] = have ? src[e] : 0.f;
 		return;
 	}
 	const float *src = x + (size_t)row * dim;
-	float mean = 0.f;
-	if (layer_norm) {
-		float s = 0.f;
-		for (int e = threadIdx.x; e < dim; e += blockDim.x) s += src[e];
-		mean = block_sum(s, red) / dim;
-	}
-	float ss = 0.f;
+	float s = 0.f;
+#pragma unroll 8
 	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
-		const float d = src[e] - mean;
+		const float v = src[e];
+		dst[e] = v;
+		s += v;
+	}
+	const float mean = layer_norm ? block_sum(s, red) / dim : 0.f;
+	float ss = 0.f;
+#pragma unroll 8
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
+		const float d = dst[e] - mean;
 		ss += d * d;
 	}
 	ss = block_sum(ss, red);
 	const float r = 1.0f / sqrtf(ss / dim + eps);
-	for (int e = threadIdx.x; e < dim; e += blockDim.x) dst[e] = (src[e] - mean) * r * w[e];
+#pragma unroll 8
+	for (int e = threadIdx.x; e < dim; e += blockDim.x) dst[e] = (dst[e] - mean) * r * w[e];
 }
 
 // One CTA per row m: the normed rows m - taps + 1 .. m are rebuilt in shared memory (rows of the call from x, earlier ones from
 // the state (taps - 1, dim), whose slot s is the normed input of position p0 - (taps - 1) + s), u = h_m + sum_j cw[:, j] h_(m-taps+1+j).
 // h_m also goes to h.  single != 0 (one-row calls): the CTA then shifts the state itself.
-__global__ void __launch_bounds__(256) norm_conv_rows_kernel(float *__restrict__ u, float *__restrict__ h, const float *__restrict__ x,
-                                                             const float *__restrict__ w, int layer_norm, float eps, const float *__restrict__ cw,
-                                                             float *state, int dim, int taps, int single, int pos0, const int *__restrict__ ctl,
-                                                             float *xadd, const float *__restrict__ add) {
+__global__ void __launch_bounds__(256) norm_conv_rows_kernel(float *__restrict__ u, float *__restrict__ h, const float *x, const float *__restrict__ w,
+                                                             int layer_norm, float eps, const float *__restrict__ cw, float *state, int dim, int taps,
+                                                             int single, int pos0, const int *__restrict__ ctl, float *xadd, const float *__restrict__ add) {
 	extern __shared__ float hs[]; // taps x dim
 	__shared__ float red[33];
 	const int m = blockIdx.x, p0 = first_pos(ctl, pos0);
 	if (add) { // one-row calls: the residual takes the previous sublayer's output first
+#pragma unroll 8
 		for (int e = threadIdx.x; e < dim; e += blockDim.x) xadd[e] += add[e];
 		__syncthreads();
 	}
 	for (int j = 0; j < taps; ++j) normed_row(hs + (size_t)j * dim, x, w, state, m - (taps - 1) + j, p0, taps, dim, layer_norm, eps, red);
 	__syncthreads();
+#pragma unroll 4
 	for (int e = threadIdx.x; e < dim; e += blockDim.x) {
 		const float hm = hs[(size_t)(taps - 1) * dim + e];
 		float acc = hm;
@@ -78,6 +87,58 @@ __global__ void __launch_bounds__(256) norm_conv_rows_kernel(float *__restrict__
 			for (int s = 0; s < taps - 1; ++s) state[(size_t)s * dim + e] = hs[(size_t)(s + 1) * dim + e];
 	}
 }
+// One-row calls (a decode step): every thread fetches its channels of x (+ add), the norm weight, the stored rows and the
+// convolution weights at once, so that the whole kernel is one memory round trip, two block sums and the stores.  EPT channels
+// per thread, at most kOneTaps taps.
+constexpr int kOneTaps = 5, kOneThreads = 1024;
+template <int EPT>
+__global__ void __launch_bounds__(kOneThreads) norm_conv_one_kernel(float *__restrict__ u, float *__restrict__ h, float *x, const float *__restrict__ add,
+                                                                    const float *__restrict__ w, int layer_norm, float eps, const float *__restrict__ cw,
+                                                                    float *state, int dim, int taps, int pos0, const int *__restrict__ ctl) {
+	__shared__ float red[33];
+	const int p0 = first_pos(ctl, pos0);
+	float xv[EPT], wv[EPT], sv[kOneTaps - 1][EPT], cv[kOneTaps][EPT];
+#pragma unroll
+	for (int i = 0; i < EPT; ++i) {
+		const int e = threadIdx.x + i * kOneThreads;
+		const bool in = e < dim;
+		xv[i] = in ? x[e] : 0.f;
+		if (add && in) xv[i] += add[e];
+		wv[i] = in ? w[e] : 0.f;
+#pragma unroll
+		for (int s = 0; s < kOneTaps - 1; ++s) sv[s][i] = (in && s < taps - 1 && p0 - (taps - 1) + s >= 0) ? state[(size_t)s * dim + e] : 0.f;
+#pragma unroll
+		for (int j = 0; j < kOneTaps; ++j) cv[j][i] = (in && j < taps) ? cw[(size_t)e * taps + j] : 0.f;
+	}
+	float s1 = 0.f;
+#pragma unroll
+	for (int i = 0; i < EPT; ++i) s1 += xv[i];
+	const float mean = layer_norm ? block_sum(s1, red) / dim : 0.f;
+	float ss = 0.f;
+#pragma unroll
+	for (int i = 0; i < EPT; ++i) {
+		const float d = threadIdx.x + i * kOneThreads < dim ? xv[i] - mean : 0.f;
+		ss += d * d;
+	}
+	ss = block_sum(ss, red);
+	const float r = 1.0f / sqrtf(ss / dim + eps);
+#pragma unroll
+	for (int i = 0; i < EPT; ++i) {
+		const int e = threadIdx.x + i * kOneThreads;
+		if (e >= dim) continue;
+		const float hm = (xv[i] - mean) * r * wv[i];
+		float acc = hm;
+#pragma unroll
+		for (int j = 0; j < kOneTaps; ++j)
+			if (j < taps) acc = fmaf(cv[j][i], j == taps - 1 ? hm : sv[j][i], acc);
+		u[e] = acc, h[e] = hm;
+		if (add) x[e] = xv[i];
+#pragma unroll
+		for (int s = 0; s < kOneTaps - 1; ++s)
+			if (s < taps - 1) state[(size_t)s * dim + e] = s + 1 == taps - 1 ? hm : sv[s + 1][i];
+	}
+}
+
 // After a call of n > 1 rows: slot s <- the normed input of row n - (taps - 1) + s (from h, or an old slot above s).
 __global__ void norm_conv_state_kernel(float *state, const float *__restrict__ h, int n, int dim, int taps, int pos0, const int *__restrict__ ctl) {
 	const int e = blockIdx.x * blockDim.x + threadIdx.x, p0 = first_pos(ctl, pos0);
@@ -162,6 +223,7 @@ __global__ void __launch_bounds__(64) latent_query_rows_kernel(float *__restrict
 		float acc[kLqRows];
 #pragma unroll
 		for (int i = 0; i < kLqRows; ++i) acc[i] = 0.f;
+#pragma unroll 8
 		for (int d = 0; d < dim; ++d) {
 			const float wv = Elem<DT>::get(uk, ((size_t)h * dim + d) * kv_rank + c);
 #pragma unroll
@@ -524,9 +586,15 @@ extern "C" int yalm_add_norm_conv_rows(float *u, float *h, float *x, const float
 		add = nullptr;
 	}
 	if (!u || !h || !x || !w || !conv_w || n < 1 || dim < 1 || taps < 1 || (taps > 1 && !state) || u == x || h == x) return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	if (n == 1 && taps <= kOneTaps && dim <= 4 * kOneThreads) {
+		if (dim <= kOneThreads) norm_conv_one_kernel<1><<<1, kOneThreads, 0, st>>>(u, h, x, add, w, layer_norm, eps, conv_w, state, dim, taps, pos0, ctl);
+		else if (dim <= 2 * kOneThreads) norm_conv_one_kernel<2><<<1, kOneThreads, 0, st>>>(u, h, x, add, w, layer_norm, eps, conv_w, state, dim, taps, pos0, ctl);
+		else norm_conv_one_kernel<4><<<1, kOneThreads, 0, st>>>(u, h, x, add, w, layer_norm, eps, conv_w, state, dim, taps, pos0, ctl);
+		return (int)cudaGetLastError();
+	}
 	const size_t smem = sizeof(float) * (size_t)taps * dim;
 	if (smem > 160 * 1024) return YALM_EINVAL;
-	cudaStream_t st = (cudaStream_t)s;
 	if (smem > 48 * 1024) YALM_TRY(cudaFuncSetAttribute(norm_conv_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	norm_conv_rows_kernel<<<n, 256, smem, st>>>(u, h, x, w, layer_norm, eps, conv_w, state, dim, taps, n == 1, pos0, ctl, x, add);
 	if (n > 1 && taps > 1) norm_conv_state_kernel<<<(dim + 255) / 256, 256, 0, st>>>(state, h, n, dim, taps, pos0, ctl);
@@ -656,7 +724,7 @@ extern "C" int yalm_attn_latent_rows(float *out, int ldo, const float *q, int ld
 	if (workspace && ctas < 296) { // few rows: split the keys so that every SM has work; the count depends on shapes only
 		const int most = window > 0 ? window : (context > 0 ? context : ring);
 		const int batches = (most + kLaWarps * kLaBatch - 1) / (kLaWarps * kLaBatch);
-		nsplit = std::max(1, std::min({(296 + ctas - 1) / ctas, batches, kLaMaxParts / (n * n_heads), 64}));
+		nsplit = std::max(1, std::min({(296 + ctas - 1) / ctas, batches, kLaMaxParts / (n * n_heads), 16}));
 	}
 	cudaStream_t st = (cudaStream_t)s;
 #define LA_CASE(R_, NP_)                                                                                                              \

@@ -70,19 +70,23 @@ __device__ __forceinline__ float warp_dot(const void *w, size_t row_off, const f
 		constexpr int U = 4, STEP = 32 * E::VEC; // U loads in flight per lane before the first multiply
 		for (int k0 = lane * E::VEC; k0 < K; k0 += U * STEP) {
 			uint4 wv[U];
+			float4 xv[U][E::VEC / 4]; // the inputs are fetched with the weights: one memory round trip per batch, not one per piece
 #pragma unroll
 			for (int u = 0; u < U; ++u)
-				if (k0 + u * STEP < K) wv[u] = ldg_stream(row + k0 + u * STEP);
+				if (k0 + u * STEP < K) {
+					wv[u] = ldg_stream(row + k0 + u * STEP);
+#pragma unroll
+					for (int i = 0; i < E::VEC / 4; ++i) xv[u][i] = *reinterpret_cast<const float4 *>(x + k0 + u * STEP + 4 * i);
+				}
 #pragma unroll
 			for (int u = 0; u < U; ++u)
 				if (k0 + u * STEP < K) {
 					float f[8];
 					E::unpack(wv[u], f);
-					const int k = k0 + u * STEP;
 #pragma unroll
-					for (int i = 0; i < E::VEC; i += 4) {
-						const float4 xv = *reinterpret_cast<const float4 *>(x + k + i);
-						acc = fmaf(f[i], xv.x, acc), acc = fmaf(f[i + 1], xv.y, acc), acc = fmaf(f[i + 2], xv.z, acc), acc = fmaf(f[i + 3], xv.w, acc);
+					for (int i = 0; i < E::VEC / 4; ++i) {
+						acc = fmaf(f[4 * i], xv[u][i].x, acc), acc = fmaf(f[4 * i + 1], xv[u][i].y, acc);
+						acc = fmaf(f[4 * i + 2], xv[u][i].z, acc), acc = fmaf(f[4 * i + 3], xv[u][i].w, acc);
 					}
 				}
 		}
