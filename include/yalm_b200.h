@@ -325,9 +325,9 @@ int yalm_add_norm_conv_rows(float *u, float *h, float *x, const float *add, cons
 int yalm_latent_post_rows(float *proj, int ld, int o_q, int q_rank, const float *q_norm, int o_kv, int kv_rank, int rot_dim, const float *kv_norm,
                           void *ring_buf, int ring, const float *freq, float magnitude, int rot_dims, int interleaved, float eps, int cache_f32,
                           int n, int pos0, const int *ctl, yalm_stream_t s);
-/* q (n, heads (dim + rot_dim)) -> out (n, heads (kv_rank + rot_dim)): per head [uk_h^T q_unrotated | rotated part turned by its
- * position], uk (heads dim, kv_rank): the query against cached rows [latent | rotated key part]. */
-int yalm_latent_query_rows(float *out, int ldo, const float *q, int ldq, const void *uk, int dtype, int n, int heads, int dim, int rot_dim,
+/* q (n, heads (dim + rot_dim)) -> out (n, heads (kv_rank + rot_dim)): per head [ukt_h q_unrotated | rotated part turned by its
+ * position], ukt (heads, kv_rank, dim) = every head's W_uk transposed: the query against cached rows [latent | rotated key part]. */
+int yalm_latent_query_rows(float *out, int ldo, const float *q, int ldq, const void *ukt, int dtype, int n, int heads, int dim, int rot_dim,
                            int kv_rank, const float *freq, float magnitude, int rot_dims, int interleaved, int pos0, const int *ctl,
                            yalm_stream_t s);
 /* Prompt portions of latent attention on the tensor cores: the cached rows (bf16) of positions first_pos .. first_pos + count - 1

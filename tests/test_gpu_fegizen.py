@@ -121,7 +121,7 @@ def test_latent_rows_norms_rotation_and_cache(scaling, sizes):
     ringbuf = torch.zeros(ring, r + dr, device="cuda")
     q = rng.standard_normal((T, H, dn + dr))
     uk = rng.standard_normal((H * dn, r))
-    qd, ukd = dev(q.reshape(T, -1)), dev(uk)
+    qd, ukd = dev(q.reshape(T, -1)), dev(uk.reshape(H, dn, r).transpose(0, 2, 1))     # the library takes every head's matrix transposed
     qa = torch.zeros(T, H * (r + dr), device="cuda")
     for at, n in portions(T, sizes):
         ok(L.yalm_latent_post_rows(ptr(Pd[at:]), ld, o_q, qr, devp((qw)), o_kv, r, dr, devp((kw)), ptr(ringbuf), ring, ptr(fd), mag, dr, 1, eps, 1, n, at, None,
@@ -154,7 +154,7 @@ def test_rotation_at_large_positions():
     q, uk = rng.standard_normal((1, dn + dr)), rng.standard_normal((dn, r))
     out = torch.zeros(1, r + dr, device="cuda")
     for pos in (0, 1, 4095, 100000):
-        ok(L.yalm_latent_query_rows(ptr(out), r + dr, devp((q)), dn + dr, devp((uk)), api.F32, 1, 1, dn, dr, r, devp((freqs)), mag, dr, 1, pos, None, None), "q rows")
+        ok(L.yalm_latent_query_rows(ptr(out), r + dr, devp((q)), dn + dr, devp((uk.T)), api.F32, 1, 1, dn, dr, r, devp((freqs)), mag, dr, 1, pos, None, None), "q rows")
         want = O.rotate_pairs(q[0, dn:], pos, freqs.astype(np.float32).astype(np.float64), mag)
         close_enough(out.cpu().numpy()[0, r:], want, 1e-5 + 2e-7 * pos)
 

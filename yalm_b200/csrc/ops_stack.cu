@@ -601,17 +601,20 @@ __global__ void glu_act_rows_kernel(float *__restrict__ h, const float *__restri
 // neighbours, a group scores its best expert, and only experts of the `keep` best groups (ties: the lower index) can be
 // chosen.  One CTA per row; E <= 1024.
 template <int DT>
-__global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ x, int ldx,
+__global__ void __launch_bounds__(256) router_topk_rows_kernel(int *__restrict__ ids, float *__restrict__ wts, const float *__restrict__ x, int ldx,
                                                                const void *__restrict__ wr, int E, int top, int dim, int score, int renorm,
                                                                float renorm_eps, int groups, int keep, bool vec, const float *__restrict__ bias,
                                                                float wscale) {
 	extern __shared__ float sc[]; // E, then E logits as they were
 	const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const float *xr = x + (size_t)m * ldx;
-	for (int e = warp; e < E; e += 4) {
+	for (int e = warp; e < E; e += (int)(blockDim.x >> 5)) {
 		const float z = warp_dot<DT>(wr, (size_t)e * dim, xr, dim, vec);
 		if (lane == 0) sc[e] = z;
 	}
+	float *ch = sc + E + groups; // E: score + bias
+	if (bias)
+		for (int e = threadIdx.x; e < E; e += blockDim.x) ch[e] = bias[e];
 	__syncthreads();
 	if (threadIdx.x == 0) {
 		// The experts are ranked by their logits: both score functions are monotonic, and in fp32 a saturated sigmoid (or an
@@ -640,10 +643,9 @@ __global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__
 		float tot = 0.f;
 		if (bias) {
 			// the choice adds a stored bias to the score, so it cannot be ranked by the logits: rank score + bias, weigh by the score
-			float *ch = sc + E + groups; // E
 			for (int e = 0; e < E; ++e) {
 				sc[e] = sc[e] == -INFINITY ? 0.f : (score == 1 ? 1.0f / (1.0f + expf(-sc[e])) : expf(sc[e] - mx) / sum);
-				ch[e] = sc[e] + bias[e];
+				ch[e] += sc[e];
 			}
 			for (int j = 0; j < top; ++j) {
 				int best = -1;
@@ -667,10 +669,15 @@ __global__ void __launch_bounds__(128) router_topk_rows_kernel(int *__restrict__
 			tot += bv;
 			sc[best] = -INFINITY;
 		}
-		if (renorm)
-			for (int j = 0; j < top; ++j) wts[(size_t)m * top + j] /= tot + renorm_eps;
-		if (wscale != 1.f)
-			for (int j = 0; j < top; ++j) wts[(size_t)m * top + j] *= wscale;
+		if (renorm || wscale != 1.f) { // both at once: the weights make one trip to memory and back
+			const float den = renorm ? tot + renorm_eps : 1.f;
+			for (int j = 0; j < top; ++j) {
+				float v = wts[(size_t)m * top + j];
+				if (renorm) v /= den;
+				if (wscale != 1.f) v *= wscale;
+				wts[(size_t)m * top + j] = v;
+			}
+		}
 	}
 }
 
@@ -952,7 +959,7 @@ extern "C" int yalm_router_bias_topk_rows(int *ids, float *wts, const float *x, 
 	    keep_groups > groups || top > keep_groups * (n_experts / groups))
 		return YALM_EINVAL;
 	const bool vec = row_vec(wr, dim, dtype) && aligned16(x) && ldx % 4 == 0;
-	DISPATCH_DT(dtype, (router_topk_rows_kernel<DT><<<n, 128, sizeof(float) * (2 * n_experts + groups), (cudaStream_t)s>>>(
+	DISPATCH_DT(dtype, (router_topk_rows_kernel<DT><<<n, n <= 4 ? 256 : 128, sizeof(float) * (2 * n_experts + groups), (cudaStream_t)s>>>(
 	                       ids, wts, x, ldx, wr, n_experts, top, dim, score, renorm, renorm_eps, groups, keep_groups, vec, bias, weight_scale)));
 	return (int)cudaGetLastError();
 }

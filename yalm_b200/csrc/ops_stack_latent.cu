@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(256) latent_post_rows_kernel(float *__restrict
 
 // ---- latent attention: the query against cached rows ------------------------------------------------------------------------
 // q (n, heads (dim + rot_dim)), per head [unrotated | rotated].  out (n, heads (kv_rank + rot_dim)):
-//   out[m, h, c] = sum_d q[m, h, d] uk[h dim + d, c]   (c < kv_rank; uk (heads dim, kv_rank) as stored: W_uk^T q)
+//   out[m, h, c] = sum_d q[m, h, d] ukt[h, c, d]   (c < kv_rank; ukt (heads, kv_rank, dim): every head's W_uk transposed)
 //   out[m, h, kv_rank + j] = the rotated part turned by position p0 + m
 // so that out[m, h] . [latent_j | key part_j] is the score of head h against position j.  One CTA per (head, block of RB rows);
 // a thread owns output channels c and walks d with the rows' queries in shared memory: neighbouring threads read neighbouring
@@ -207,28 +207,51 @@ __global__ void __launch_bounds__(256) latent_post_rows_kernel(float *__restrict
 constexpr int kLqRows = 8;
 template <int DT>
 __global__ void __launch_bounds__(64) latent_query_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
-                                                                const void *__restrict__ uk, int n, int dim, int rot_dim, int kv_rank,
+                                                                const void *__restrict__ ukt, int n, int dim, int rot_dim, int kv_rank,
                                                                 const float *__restrict__ freq, float mag, int rot_dims, int interleaved, int pos0,
                                                                 const int *__restrict__ ctl) {
 	extern __shared__ float qs[]; // kLqRows x (dim + rot_dim)
 	const int h = blockIdx.x, m0 = blockIdx.y * kLqRows, mb = min(kLqRows, n - m0), dq = dim + rot_dim, p0 = first_pos(ctl, pos0);
+#pragma unroll 4
 	for (int e = threadIdx.x; e < kLqRows * dq; e += blockDim.x) {
 		const int i = e / dq, d = e % dq;
 		qs[e] = i < mb ? q[(size_t)(m0 + i) * ldq + (size_t)h * dq + d] : 0.f;
 	}
 	__syncthreads();
 	const size_t obase = (size_t)h * (kv_rank + rot_dim);
-	// grid.z cuts the output channels into pieces of one per thread: a decode row then still fills the GPU
+	// grid.z cuts the output channels into pieces of one per thread: a decode row then still fills the GPU.  The weights are
+	// stored transposed, (heads, kv_rank, dim): an output channel's weights are one contiguous row, fetched as 16-byte pieces
+	// that are all in flight at once.
+	const bool vec = dim % Elem<DT>::VEC == 0 && aligned16(ukt) && dim <= 16 * Elem<DT>::VEC;
 	for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < kv_rank; c += gridDim.z * blockDim.x) {
 		float acc[kLqRows];
 #pragma unroll
 		for (int i = 0; i < kLqRows; ++i) acc[i] = 0.f;
-#pragma unroll 8
-		for (int d = 0; d < dim; ++d) {
-			const float wv = Elem<DT>::get(uk, ((size_t)h * dim + d) * kv_rank + c);
+		const size_t roff = ((size_t)h * kv_rank + c) * dim;
+		if (vec) {
+			using T = typename Elem<DT>::T;
+			constexpr int V = Elem<DT>::VEC;
+			const T *wr = static_cast<const T *>(ukt) + roff;
+			uint4 wv[16];
 #pragma unroll
-			for (int i = 0; i < kLqRows; ++i) acc[i] = fmaf(wv, qs[i * dq + d], acc[i]);
-		}
+			for (int k = 0; k < 16; ++k)
+				if (k * V < dim) wv[k] = __ldg(reinterpret_cast<const uint4 *>(wr + k * V));
+#pragma unroll
+			for (int k = 0; k < 16; ++k)
+				if (k * V < dim) {
+					float f[8];
+					Elem<DT>::unpack(wv[k], f);
+#pragma unroll
+					for (int j = 0; j < V; ++j)
+#pragma unroll
+						for (int i = 0; i < kLqRows; ++i) acc[i] = fmaf(f[j], qs[i * dq + k * V + j], acc[i]);
+				}
+		} else
+			for (int d = 0; d < dim; ++d) {
+				const float wv = Elem<DT>::get(ukt, roff + d);
+#pragma unroll
+				for (int i = 0; i < kLqRows; ++i) acc[i] = fmaf(wv, qs[i * dq + d], acc[i]);
+			}
 #pragma unroll
 		for (int i = 0; i < kLqRows; ++i)
 			if (i < mb) out[(size_t)(m0 + i) * ldo + obase + c] = acc[i];
@@ -404,6 +427,7 @@ __global__ void __launch_bounds__(kLaWarps * 32) attn_latent_rows_kernel(float *
 	const int h0 = blockIdx.x * R, nh = min(R, n_heads - h0), m = blockIdx.y, z = blockIdx.z, nsplit = gridDim.z;
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int i = first_pos(ctl, pos0) + m, lo = window > 0 ? max(0, i - window + 1) : 0, ntok = i - lo + 1;
+#pragma unroll 8
 	for (int e = threadIdx.x; e < R * dkp; e += blockDim.x) {
 		const int r = e / dkp, d = e % dkp;
 		qs[e] = (r < nh && d < dk) ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
@@ -517,22 +541,35 @@ __global__ void __launch_bounds__(kLaWarps * 32) attn_latent_rows_kernel(float *
 // out[m, h, :] = sum_z w_z acc_z / sum_z w_z L_z with w_z = exp(M_z - max M), splits taken in order (a split without keys has
 // M = -inf and no weight).  grid (heads, rows).
 __global__ void attn_latent_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, int n_heads, int dv, int nsplit) {
+	__shared__ float wz[64]; // the splits' weights over the common sum (nsplit <= 64)
 	const int h = blockIdx.x, m = blockIdx.y;
 	const float *pr = part + (size_t)(m * n_heads + h) * nsplit * (dv + 2);
-	float M = -INFINITY;
-	for (int z = 0; z < nsplit; ++z) M = fmaxf(M, pr[(size_t)z * (dv + 2) + dv]);
-	float L = 0.f;
-	for (int z = 0; z < nsplit; ++z) {
-		const float mz = pr[(size_t)z * (dv + 2) + dv];
-		if (mz != -INFINITY) L += expf(mz - M) * pr[(size_t)z * (dv + 2) + dv + 1];
+	if (threadIdx.x < 32) { // lane = split
+		const int lane = threadIdx.x;
+		float mz[2], lz[2];
+#pragma unroll
+		for (int k = 0; k < 2; ++k) {
+			const int z = lane + 32 * k;
+			mz[k] = z < nsplit ? pr[(size_t)z * (dv + 2) + dv] : -INFINITY;
+			lz[k] = z < nsplit ? pr[(size_t)z * (dv + 2) + dv + 1] : 0.f;
+		}
+		const float M = warp_max(fmaxf(mz[0], mz[1]));
+		float e[2];
+#pragma unroll
+		for (int k = 0; k < 2; ++k) e[k] = mz[k] == -INFINITY ? 0.f : expf(mz[k] - M);
+		// the sum runs over the splits in order
+		float L = 0.f;
+		for (int z = 0; z < nsplit; ++z) L += __shfl_sync(kFull, z < 32 ? e[0] * lz[0] : e[1] * lz[1], z & 31);
+#pragma unroll
+		for (int k = 0; k < 2; ++k)
+			if (lane + 32 * k < nsplit) wz[lane + 32 * k] = e[k] / L;
 	}
+	__syncthreads();
 	for (int c = threadIdx.x; c < dv; c += blockDim.x) {
 		float o = 0.f;
-		for (int z = 0; z < nsplit; ++z) {
-			const float mz = pr[(size_t)z * (dv + 2) + dv];
-			if (mz != -INFINITY) o += expf(mz - M) * pr[(size_t)z * (dv + 2) + c];
-		}
-		out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+#pragma unroll 8
+		for (int z = 0; z < nsplit; ++z) o = fmaf(wz[z], pr[(size_t)z * (dv + 2) + c], o);
+		out[(size_t)m * ldo + (size_t)h * dv + c] = o;
 	}
 }
 

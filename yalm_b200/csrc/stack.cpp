@@ -73,6 +73,7 @@ struct StackLayer {
 	// latent attention: columns [query latent | key / value latent + shared key part (own cache only) | gate]
 	int o_kv = 0, kv_owner = -1;                              // kv_owner: the layer whose ring this layer reads (itself, or kv_from)
 	void *wuq = nullptr, *wuk = nullptr, *wuv = nullptr;      // (heads (dim + rot), q_rank), (heads dim, kv_rank), (heads vdim, kv_rank)
+	void *wukt = nullptr;                                     // (heads, kv_rank, dim): every head's W_uk transposed, for the queries against cached rows
 	float *rot_freq = nullptr;                                // rotary frequencies (rot dims / 2)
 	float rot_mag = 1.f;
 	// gated linear attention: columns [q | k | v | gate | decay stage 1]; wa2, d_dt_bias (the decay's bias), mix_norm, scan_state as above
@@ -412,6 +413,18 @@ void Model::build_stack(YALMData &data) {
 					pl.push_back({&L->wuk, {mat(tensor(i, TensorRole::LatentUk, -1, {m.heads * m.dim, a.kv_rank})), mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
 				else
 					pl.push_back({&L->wuv, {mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
+				if (m.dim > 0) { // the same matrix, each head transposed: an output channel of W_uk^T q is then one contiguous row
+					const auto uk = mat(tensor(i, TensorRole::LatentUk, -1, {m.heads * m.dim, a.kv_rank}));
+					const size_t es = dtype_size(dt);
+					_host_converted.emplace_back(uk.second);
+					char *t = _host_converted.back().data();
+					const char *src = static_cast<const char *>(uk.first);
+					for (int hh = 0; hh < m.heads; ++hh)
+						for (int d = 0; d < m.dim; ++d)
+							for (int cc = 0; cc < a.kv_rank; ++cc)
+								memcpy(t + (((size_t)hh * a.kv_rank + cc) * m.dim + d) * es, src + (((size_t)hh * m.dim + d) * a.kv_rank + cc) * es, es);
+					pl.push_back({&L->wukt, {{t, uk.second}}});
+				}
 				pl.push_back({&L->wo, {mat(tensor(i, TensorRole::Wo, -1, {W, no}))}});
 				if (a.rot.dims > 0) {
 					std::vector<float> fr;
@@ -895,7 +908,7 @@ int Model::stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int i
 			                                 m.scale, pos0, ctl, st));
 			if (m.out_gate) ST_TRY(yalm_sigmoid_gate_rows(S.att, no, P + L.o_gate, ldp, n, no, st));
 		} else {
-		ST_TRY(yalm_latent_query_rows(S.aux, nqa, S.conv, nq, L.wuk, dt, n, m.heads, m.dim, a.rot_dim, a.kv_rank, L.rot_freq, L.rot_mag, a.rot.dims,
+		ST_TRY(yalm_latent_query_rows(S.aux, nqa, S.conv, nq, L.wukt, dt, n, m.heads, m.dim, a.rot_dim, a.kv_rank, L.rot_freq, L.rot_mag, a.rot.dims,
 		                              a.rot.interleaved ? 1 : 0, pos0, ctl, st));
 		// every head reads the one row of a position: keys are whole rows, values their first kv_rank channels
 		static const bool one_pass_off = [] { const char *e = getenv("YALM_STACK_ATTN_LANES"); return e && e[0] == '0'; }();
