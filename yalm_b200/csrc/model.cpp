@@ -118,6 +118,22 @@ size_t Config::active_bytes(size_t pos) const {
 				if (l.ffn.kind == yalm::FfnSpec::Moe) total += ((size_t)l.ffn.experts * W + (size_t)l.ffn.top * 3 * l.ffn.ff * W) * ws;
 				continue;
 			}
+			if (l.kind == yalm::MixerKind::LatentAttention || l.kind == yalm::MixerKind::LinearAttention) {
+				// the packed projection and the output projection, the per-head maps, the window of cached rows (one row per position for
+				// all heads) or the fp32 matrix state read and written; the chosen experts, the router and the shared expert
+				total += ((size_t)l.proj_width() + (l.kind == yalm::MixerKind::LatentAttention ? (size_t)m.heads * m.vdim : (size_t)l.gla.heads * l.gla.vdim)) * W * ws +
+				         4 * W * 4;
+				if (l.kind == yalm::MixerKind::LatentAttention) {
+					const yalm::LatentSpec &a = l.latent;
+					total += ((size_t)m.heads * (m.dim + a.rot_dim) * a.q_rank + (size_t)m.heads * (m.dim + m.vdim) * a.kv_rank) * ws;
+					total += (m.window > 0 ? std::min<size_t>(pos + 1, m.window) : pos + 1) * (a.kv_rank + a.rot_dim) * cb;
+				} else
+					total += (size_t)l.gla.decay_rank * l.gla.heads * l.gla.dim * ws + (size_t)2 * 4 * l.gla.heads * l.gla.dim * l.gla.vdim;
+				if (l.ffn.kind == yalm::FfnSpec::Dense) total += (size_t)3 * l.ffn.ff * W * ws;
+				else if (l.ffn.kind == yalm::FfnSpec::Moe)
+					total += ((size_t)(l.ffn.experts + l.ffn.identity) * W + (size_t)l.ffn.top * 3 * l.ffn.ff * W + (size_t)3 * l.ffn.shared_ff * W) * ws;
+				continue;
+			}
 			const size_t nq = (size_t)m.heads * m.dim, nk = (size_t)m.kv_heads * m.dim, nv = (size_t)m.kv_heads * m.vdim, no = (size_t)m.heads * m.vdim;
 			total += (nq + nk + nv + no) * W * ws + (nq + nk + 2 * W) * 4;
 			const size_t seen = m.window > 0 ? std::min<size_t>(pos + 1, m.window) : pos + 1;
@@ -834,6 +850,9 @@ int Model::launches_per_forward(InferenceMode mode) const {
 		for (const yalm::LayerSpec &l : config->stack->layers) {
 			if (config->stack->parallel_block) // norm + shift, projection, mixer (state space 5, parallel 14), experts 3, residual
 				n += 3 + (l.kind == yalm::MixerKind::StateSpace ? 5 : 14) + (l.ffn.kind == yalm::FfnSpec::None ? 0 : 3);
+			else if (l.kind == yalm::MixerKind::LatentAttention || l.kind == yalm::MixerKind::LinearAttention) // norm + conv, projection, mixer (8 / 5), norm + conv, feed-forward (3, or 3 + 3 with a shared expert), depth sum
+				n += 2 + (l.kind == yalm::MixerKind::LatentAttention ? 8 : 5) + 1 +
+				     (l.ffn.kind == yalm::FfnSpec::None ? 0 : 1 + (l.ffn.kind == yalm::FfnSpec::Dense ? 3 : 3 + (l.ffn.shared_ff > 0 ? 3 : 0)));
 			else
 				n += 5 + (l.mix.pool > 0 ? 1 : 0) + (l.ffn.kind == yalm::FfnSpec::None ? 0 : 4);
 		}
