@@ -482,6 +482,74 @@ def test_shared_cache_with_a_wider_window_than_its_owner(tmp_path):
     close_enough(dec, want[3:])
 
 
+def test_sizes_that_are_no_vector_multiple(tmp_path):
+    """Width, vocabulary, latent and head sizes that are not multiples of 4 or 8: every product and row op on its scalar route."""
+    cfg = O.make_config([
+        ("latent_attention", O.latent_mixer(heads=3, dim=7, rot_dim=6, vdim=5, kv_rank=11, q_rank=9, window=8), O.moe_mlp(ff=10, experts=3, identity=1, top=2, shared=7)),
+        ("gla", O.gla_mixer(heads=3, dim=9, vdim=7, tau=2.0), O.dense_mlp(ff=13)),
+        ("latent_attention", O.latent_mixer(heads=2, dim=5, rot_dim=6, vdim=9, kv_rank=11, q_rank=6, window=20, kv_from=0), None),
+    ], width=50, vocab=70, taps=2)
+    folder, W = checkpoint(tmp_path, cfg, seed=21, a_rank=3, router_gain=4.0)
+    T = 60
+    toks = tokens_for(cfg, T)
+    want, after = O.forward(cfg, W, toks)
+    for dtype, tol in ((api.F32, F32_TOL), (api.BF16, 6e-2)):
+        m, s = open_model(folder, dtype)
+        whole = s.forward_rows(toks, 0, range(T))
+        s.end_sequence()
+        s.forward_rows(toks[:31], 0, [])
+        dec = np.concatenate([s.forward_rows(toks[i:i + 1], i, [0]) for i in range(31, T)])
+        close(m, s)
+        close_enough(whole, want, tol)
+        close_enough(dec, want[31:], tol)
+
+
+def test_keys_and_values_written_out_per_head():
+    """The prompt route's helpers: latents of a row range gathered from the ring, then per-head rings of [unrotated key | rotated
+    key part] and values; the in-place rotation of the queries and the gate."""
+    L = api.lib()
+    L.yalm_latent_gather_rows16.argtypes = [vp, vp, i32, i32, i32, i32, i32, vp]
+    L.yalm_latent_pack_rings.argtypes = [vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+    L.yalm_rotate_heads_rows.argtypes = [vp, i32, i32, i32, i32, vp, f32, i32, i32, i32, i32, vp, vp]
+    L.yalm_sigmoid_gate_rows.argtypes = [vp, i32, vp, i32, i32, i32, vp]
+    rng = np.random.default_rng(9)
+    ring, r, dr, H, dn, dv, ring_out = 24, 16, 6, 3, 10, 5, 40
+    first, count = 30, 20                                                    # positions 30 .. 49: slots wrap in both rings
+    rows = O.bf16_round(rng.standard_normal((ring, r + dr)))
+    ringbuf = dev(rows, torch.bfloat16)
+    lat = torch.zeros(count, r, device="cuda", dtype=torch.bfloat16)
+    ok(L.yalm_latent_gather_rows16(ptr(lat), ptr(ringbuf), ring, r + dr, r, first, count, None), "latent_gather_rows16")
+    want_lat = np.stack([rows[(first + j) % ring, :r] for j in range(count)])
+    np.testing.assert_array_equal(lat.float().cpu().numpy(), want_lat)
+    kv = rng.standard_normal((count, H * (dn + dv)))
+    kout = torch.zeros(H, ring_out, dn + dr, device="cuda", dtype=torch.bfloat16)
+    vout = torch.zeros(H, ring_out, dv, device="cuda", dtype=torch.bfloat16)
+    ok(L.yalm_latent_pack_rings(ptr(kout), ptr(vout), devp((kv)), H * (dn + dv), ptr(ringbuf), ring, r, dr, H, dn, dv, ring_out, first, count, None), "latent_pack_rings")
+    kg, vg = kout.float().cpu().numpy(), vout.float().cpu().numpy()
+    for j in range(count):
+        p = first + j
+        for h in range(H):
+            np.testing.assert_array_equal(kg[h, p % ring_out, :dn], O.bf16_round(kv[j, h * dn:(h + 1) * dn]))
+            np.testing.assert_array_equal(kg[h, p % ring_out, dn:], rows[p % ring, r:])
+            np.testing.assert_array_equal(vg[h, p % ring_out], O.bf16_round(kv[j, H * dn + h * dv:H * dn + (h + 1) * dv]))
+    freqs, mag = O.rotary_table({"dims": 4, "base": 50.0, "scaling": {"factor": 2.0, "original": 8, "fast": 4.0, "slow": 1.0}})
+    n, hs = 7, dn + dr
+    q = rng.standard_normal((n, H, hs))
+    qd = dev(q.reshape(n, -1))
+    ok(L.yalm_rotate_heads_rows(ptr(qd), H * hs, H, hs, dn, devp((freqs)), mag, 4, 1, n, 100, None, None), "rotate_heads_rows")
+    want = q.copy()
+    for t in range(n):
+        for h in range(H):
+            want[t, h, dn:] = O.rotate_pairs(q[t, h, dn:], 100 + t, freqs, mag)      # 4 of the 6 channels turn, 2 pass unchanged
+    close_enough(qd.cpu().numpy().reshape(n, H, hs), want, 1e-5)
+    x, g = rng.standard_normal((n, 11)), rng.standard_normal((n, 13))
+    xd = dev(x)
+    ok(L.yalm_sigmoid_gate_rows(ptr(xd), 11, devp((g)), 13, n, 9, None), "sigmoid_gate_rows")
+    want = x.copy()
+    want[:, :9] /= 1 + np.exp(-g[:, :9])
+    close_enough(xd.cpu().numpy(), want, 1e-6)
+
+
 def test_whole_prompt_decoding_and_portions_agree(tmp_path):
     cfg = five_layers()
     folder, W = checkpoint(tmp_path, cfg, seed=5, router_gain=4.0)

@@ -761,7 +761,7 @@ extern "C" int yalm_attn_latent_rows(float *out, int ldo, const float *q, int ld
 	if (workspace && ctas < 296) { // few rows: split the keys so that every SM has work; the count depends on shapes only
 		const int most = window > 0 ? window : (context > 0 ? context : ring);
 		const int batches = (most + kLaWarps * kLaBatch - 1) / (kLaWarps * kLaBatch);
-		nsplit = std::max(1, std::min({(296 + ctas - 1) / ctas, batches, kLaMaxParts / (n * n_heads), 16}));
+		nsplit = std::max(1, std::min({(296 + ctas - 1) / ctas, batches, kLaMaxParts / (n * n_heads), 32}));
 	}
 	cudaStream_t st = (cudaStream_t)s;
 #define LA_CASE(R_, NP_)                                                                                                              \
