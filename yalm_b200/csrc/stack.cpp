@@ -9,7 +9,9 @@
 // key ring and a value ring of `ring` slots (slot = position % ring; ring = window + chunk capacity for windowed layers
 // instead of the whole context, because a token that has left every window and whose block mean is taken is dead), plus,
 // for pooled layers, one fp32 mean key / value per completed block of tokens.  A sequence restarts at position 0 and may
-// only advance: the rings cannot seek.
+// only advance: the rings cannot seek.  Layers with other state (previous rows, convolution tails, matrix states, a ring of
+// latent rows that all heads — and possibly several layers — read) list it in StackLayer::state_allocs; it is taken from the
+// same arena.
 #include "arch.h"
 #include "loader.h"
 #include "yalm_api.h"
@@ -908,17 +910,18 @@ int Model::stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int i
 			                                 m.scale, pos0, ctl, st));
 			if (m.out_gate) ST_TRY(yalm_sigmoid_gate_rows(S.att, no, P + L.o_gate, ldp, n, no, st));
 		} else {
-		ST_TRY(yalm_latent_query_rows(S.aux, nqa, S.conv, nq, L.wukt, dt, n, m.heads, m.dim, a.rot_dim, a.kv_rank, L.rot_freq, L.rot_mag, a.rot.dims,
-		                              a.rot.interleaved ? 1 : 0, pos0, ctl, st));
-		// every head reads the one row of a position: keys are whole rows, values their first kv_rank channels
-		static const bool one_pass_off = [] { const char *e = getenv("YALM_STACK_ATTN_LANES"); return e && e[0] == '0'; }();
-		if (!f32 && !one_pass_off && yalm_attn_latent_rows_shape(row, a.kv_rank, row) && ((uintptr_t)L.kring & 15) == 0 && nqa % 4 == 0)
-			ST_TRY(yalm_attn_latent_rows(S.scan, nl, S.aux, nqa, L.kring, row, S.attn_ws, n, m.heads, row, a.kv_rank, L.ring, m.window, m.scale, c.max_seq_len, pos0,
-			                             ctl, st));
-		else
-		ST_TRY(yalm_attn_window_pool_strided(S.scan, nl, S.aux, nqa, L.kring, row, L.kring, row, nullptr, nullptr, S.attn_ws, n, m.heads, 1, row, a.kv_rank,
-		                                     L.ring, 0, m.window, 0, m.scale, f32, c.max_seq_len, pos0, ctl, st));
-		ST_TRY(yalm_head_linear_gate_rows(S.att, no, S.scan, nl, L.wuv, dt, m.out_gate ? P + L.o_gate : nullptr, ldp, n, m.heads, m.vdim, a.kv_rank, st));
+			// A decode row (and what the tensor-core route does not take): W_uk moves to the query side, every head reads the one cached
+			// row of a position — keys are whole rows, values their first kv_rank channels — and W_uv follows the weighted sum.
+			ST_TRY(yalm_latent_query_rows(S.aux, nqa, S.conv, nq, L.wukt, dt, n, m.heads, m.dim, a.rot_dim, a.kv_rank, L.rot_freq, L.rot_mag, a.rot.dims,
+			                              a.rot.interleaved ? 1 : 0, pos0, ctl, st));
+			static const bool one_pass_off = [] { const char *e = getenv("YALM_STACK_ATTN_LANES"); return e && e[0] == '0'; }();
+			if (!f32 && !one_pass_off && yalm_attn_latent_rows_shape(row, a.kv_rank, row) && ((uintptr_t)L.kring & 15) == 0 && nqa % 4 == 0)
+				ST_TRY(yalm_attn_latent_rows(S.scan, nl, S.aux, nqa, L.kring, row, S.attn_ws, n, m.heads, row, a.kv_rank, L.ring, m.window, m.scale, c.max_seq_len,
+				                             pos0, ctl, st));
+			else
+				ST_TRY(yalm_attn_window_pool_strided(S.scan, nl, S.aux, nqa, L.kring, row, L.kring, row, nullptr, nullptr, S.attn_ws, n, m.heads, 1, row, a.kv_rank,
+				                                     L.ring, 0, m.window, 0, m.scale, f32, c.max_seq_len, pos0, ctl, st));
+			ST_TRY(yalm_head_linear_gate_rows(S.att, no, S.scan, nl, L.wuv, dt, m.out_gate ? P + L.o_gate : nullptr, ldp, n, m.heads, m.vdim, a.kv_rank, st));
 		}
 		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, no, L.wo, n, W, no, 1.f, st));
 	} else {
@@ -1070,9 +1073,10 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 		ST_TRY(tap());
 	}
 	if (n_want > 0) {
-		if (sp.layer_norm) ST_TRY(yalm_layer_norm_gather_rows(S.xn, S.x, from_ctl ? nullptr : S.want, rms_final_weight, 1, sp.norm_eps, n_want, W, st));
+		if (sp.layer_norm)
+			ST_TRY(yalm_layer_norm_gather_rows(S.xn, S.x, from_ctl ? nullptr : S.want, rms_final_weight, 1, sp.norm_eps, n_want, W, st));
 		else
-		ST_TRY(yalm_norm_gather_rows(S.xn, S.x, from_ctl ? nullptr : S.want, rms_final_weight, sp.norm_scalar, woff, sp.norm_eps, n_want, W, st));
+			ST_TRY(yalm_norm_gather_rows(S.xn, S.x, from_ctl ? nullptr : S.want, rms_final_weight, sp.norm_scalar, woff, sp.norm_eps, n_want, W, st));
 		// a single wanted row lands directly where the samplers read it
 		float *dst = n_want == 1 ? s.logits_dev() : S.logits;
 		ST_TRY(stack_linear(*this, c, S.a16, dst, sp.vocab, S.xn, W, wcls, n_want, sp.vocab, W, sp.logit_scale, st));
