@@ -192,7 +192,7 @@ def run_attention(q, rows, dv, window, scale, ring, sizes, cache_f32=1):
     return out.cpu().numpy().reshape(T, H, dv)
 
 
-@pytest.mark.parametrize("dk,dv,H", [(20, 12, 3), (160, 128, 8), (72, 64, 5), (13, 7, 1)])
+@pytest.mark.parametrize("dk,dv,H", [(20, 12, 3), (176, 144, 6), (72, 64, 5), (13, 7, 1)])
 @pytest.mark.parametrize("sizes", [[1000], [1], [2], [7, 1, 30]])
 def test_attention_edges_of_the_window(dk, dv, H, sizes):
     """Query i points at one key: the oldest inside the window, the newest outside, position 0, itself.  A window one key
@@ -243,7 +243,7 @@ def run_attention_one_pass(q, rows, dv, window, scale, ring, sizes):
     return out.cpu().numpy().reshape(T, H, dv)
 
 
-@pytest.mark.parametrize("dk,dv,H", [(24, 16, 3), (160, 128, 8), (320, 256, 2), (576, 512, 5), (72, 57, 1)])
+@pytest.mark.parametrize("dk,dv,H", [(24, 16, 3), (176, 144, 6), (320, 256, 2), (576, 512, 5), (72, 57, 1)])
 @pytest.mark.parametrize("sizes", [[1000], [1], [2, 1, 30]])
 def test_one_pass_attention_edges_of_the_window(dk, dv, H, sizes):
     """The same crafted queries through the kernel that serves bf16 caches; rows are bf16 values, so the comparison is exact
@@ -304,7 +304,7 @@ def run_gla(q, k, v, alpha, sizes):
     return out.cpu().numpy().reshape(T, H, P)
 
 
-@pytest.mark.parametrize("D,P,H", [(16, 24, 2), (32, 64, 6), (20, 9, 3), (128, 40, 1)])
+@pytest.mark.parametrize("D,P,H", [(16, 24, 2), (32, 72, 5), (20, 9, 3), (128, 40, 1)])
 @pytest.mark.parametrize("sizes", [[1000], [1], [2, 1, 9, 30]])
 def test_gated_linear_attention_recurrence(D, P, H, sizes):
     L = api.lib()
@@ -344,7 +344,7 @@ def test_gated_linear_attention_keeps_a_far_key():
 
 
 # ---- router, weighted sum over depth ------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("E,ident,top", [(5, 2, 2), (12, 4, 3), (3, 0, 3), (1, 1, 1)])
+@pytest.mark.parametrize("E,ident,top", [(5, 2, 2), (11, 3, 4), (3, 0, 3), (1, 1, 1)])
 def test_router_with_choice_bias(E, ident, top):
     L = api.lib()
     L.yalm_router_bias_topk_rows.argtypes = [vp, vp, vp, i32, vp, i32, i32, i32, i32, i32, i32, i32, f32, i32, i32, vp, f32, vp]

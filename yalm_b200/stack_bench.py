@@ -272,7 +272,7 @@ def write_fegizen(folder, z):
     W, taps = z["width"], 4
     mlp = {"kind": "moe", "expert": {"ff": z["moe_ff"]}, "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"], "scale": 1.0},
            "shared": {"ff": z["shared"]}}
-    rot = {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
     lat = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"], "q_rank": z["q_rank"],
            "mask": {"size": z["window"]}, "rot": rot, "scale": (z["dim"] + z["rot"]) ** -0.5}
     gla = {"heads": z["gheads"], "dim": z["gdim"], "vdim": z["gvdim"], "tau": 16.0}
