@@ -1,5 +1,5 @@
 #!/usr/bin/env python3
-"""Condense an .ncu-rep (ncu --set full --import-source on) into a text summary for profiles/.
+"""Condense an .ncu-rep (ncu --set full) into a text summary of its counters for profiles/.
 
 usage: tools/ncu_summary.py gpurun_out/mega_full.ncu-rep profiles/r1b_mega_full_summary.txt
 """
