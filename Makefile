@@ -18,7 +18,7 @@ MEGA_SRCS := $(CSRC)/decode_mega_f32.cu $(CSRC)/decode_mega_f16.cu $(CSRC)/decod
 # ... and everything else: per-op kernels, prefill, the layered executor, loader, C ABI
 CORE_SRCS := $(CSRC)/ops_gemv.cu $(CSRC)/ops_attn.cu $(CSRC)/decode_mega.cu $(CSRC)/model.cpp $(CSRC)/codec.cpp $(CSRC)/capi.cpp \
             $(CSRC)/mem.cpp $(CSRC)/tp.cpp $(CSRC)/loader.cpp $(CSRC)/prefill_gemm.cu $(CSRC)/prefill.cu $(CSRC)/ops_sample.cu $(CSRC)/sampler.cpp $(CSRC)/tokenizer.cpp \
-            $(CSRC)/arch.cpp $(CSRC)/stack.cpp $(CSRC)/ops_stack.cu $(CSRC)/ops_stack_attn.cu $(CSRC)/ops_stack_gemv.cu $(CSRC)/ops_stack_state.cu $(CSRC)/ops_stack_latent.cu
+            $(CSRC)/arch.cpp $(CSRC)/stack.cpp $(CSRC)/ops_stack.cu $(CSRC)/ops_stack_attn.cu $(CSRC)/ops_stack_gemv.cu $(CSRC)/ops_stack_state.cu $(CSRC)/ops_stack_latent.cu $(CSRC)/ops_stack_diff.cu
 LIB_SRCS := $(CORE_SRCS) $(MEGA_SRCS)
 LIB_OBJS := $(patsubst $(CSRC)/%,$(BUILD)/%.o,$(LIB_SRCS))
 # make core -> the same library without the whole-token kernel (models then run on the per-op kernels): what a layered

@@ -380,6 +380,42 @@ int yalm_moe_identity_slots(float *y, int ldy, const float *x, int ldx, const in
 int yalm_moe_down_slots_real(float *y, int ldy, const float *h, const void *wd, int dtype, const int *ids, const float *wts, int n, int top, int ff,
                              int dim, int out_scale, int n_real, const float *x, int ldx, yalm_stream_t s);
 
+/* ---- layers with a norm before and after every sublayer (csrc/ops_stack_diff.cu) and what their mixers add to the attention ops ----
+ * The attention ops with a sink per query head in the softmax's denominator (exp(sink_h) counts once, without key or value;
+ * sink NULL: none) and with v_heads value heads for n_kv key heads: key head g reads value head g % v_heads, so that several
+ * maps share one set of values.  The pooled blocks visible to a row are capped at max_blocks: with pool = 1 and max_blocks = k
+ * they are a window's kept first k tokens. */
+int yalm_attn_window_pool_sink(float *out, int ldo, const float *q, int ldq, const void *key_ring, int ldk, const void *value_ring, int ldv,
+                               const float *key_pool, const float *value_pool, float *workspace, int n, int n_heads, int n_kv, int dk, int dv,
+                               int ring, int max_blocks, int window, int pool, float scale, int cache_f32, int context, int pos0, const int *ctl,
+                               const float *sink, int v_heads, yalm_stream_t s);
+int yalm_attn_window_pool_mma_sink(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring,
+                                   const float *key_pool, const float *value_pool, int n, int n_heads, int n_kv, int dk, int dv, int ring,
+                                   int max_blocks, int window, int pool, float scale, int pos0, const int *ctl, const float *sink, int v_heads,
+                                   yalm_stream_t s);
+int yalm_attn_latent_rows_sink(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *workspace, int n, int n_heads, int dk,
+                               int dv, int ring, int window, float scale, int context, int pos0, const int *ctl, const float *sink, yalm_stream_t s);
+/* Row m of proj (ld): n_q_vectors query vectors of dk channels from o_q, n_k_vectors key vectors from o_k, n_v_heads value heads
+ * of dv channels from o_v.  Every query / key vector: RMS norm over its dk channels with the shared weight q_norm / k_norm (dk
+ * floats; NULL: none), then its first rot_dims channels turned by the row's position (freq: rot_dims / 2 frequencies, magnitude
+ * on cos and sin; pair i = channels (i, i + rot_dims / 2), or (2 i, 2 i + 1) if interleaved).  Queries stay in place, keys and
+ * values go to the rings (vector, slot, channel), slot = position % ring; positions below `keep` also to key_first (vector,
+ * keep, dk) / value_first (head, keep, dv), fp32, as the rings hold them.  dk <= 512. */
+int yalm_head_norm_rope_append_rows(float *proj, int ld, int o_q, int o_k, int o_v, int n_q_vectors, int n_k_vectors, int n_v_heads, int dk, int dv,
+                                    const float *q_norm, const float *k_norm, const float *freq, float magnitude, int rot_dims, int interleaved,
+                                    float eps, void *key_ring, void *value_ring, int ring, float *key_first, float *value_first, int keep,
+                                    int cache_f32, int n, int pos0, const int *ctl, yalm_stream_t s);
+/* maps (n, 2 heads dv): every head's first map, then every head's second.  out[m, h] = o / sqrt(mean o^2 + eps) * out_scale
+ * * sigmoid(gate[m, h]) with o = map_1 - lambda map_2 (gate NULL: none). */
+int yalm_diff_combine_rows(float *out, int ldo, const float *maps, int ldm, const float *gate, int ldg, int n, int heads, int dv, float lambda,
+                           float out_scale, float eps, yalm_stream_t s);
+/* h[m, :ff] = act(h[m, :ff]) in place; act: YALM_ACT_GELU, YALM_ACT_SILU, 3 = tanh GELU, 4 = exact (erf) GELU. */
+int yalm_act_rows(float *h, int ld, int n, int ff, int act, yalm_stream_t s);
+/* x[m] += y / sqrt(mean y^2 + eps) * norm_w, y = w_proj (gelu_tanh(w_gate x[m]) * e), e = table[token of row m, col0 .. col0 + side):
+ * w_gate (side, dim), w_proj (dim, side), table (vocab, ldt) in `dtype`; tokens (n) or, if NULL, ctl[0]. */
+int yalm_token_side_rows(float *x, const void *table, int ldt, int col0, const int *tokens, const int *ctl, const void *w_gate, const void *w_proj,
+                         const float *norm_w, int dtype, int n, int dim, int side, float eps, yalm_stream_t s);
+
 /* ---- (3a) host-pointer test entry points (src/infer.cu:890-1007 semantics) ------------------- */
 int yalm_matmul_host(float *xout, const float *x, const void *w, const float *scale, int n, int d, int dtype);
 int yalm_mha_host(float *xout, float *att, const uint16_t *kb, const uint16_t *vb, const float *q, int head_dim,

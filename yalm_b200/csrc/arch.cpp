@@ -153,7 +153,7 @@ int StackSpec::max_v_dim() const {
 int StackSpec::max_o_dim() const {
 	int m = 0;
 	for (const LayerSpec &l : layers)
-		m = std::max({m, l.mix.heads * l.mix.vdim, l.ssm.inner(), l.delta.heads * l.delta.vdim, l.mix.heads * l.latent.kv_rank, l.gla.heads * l.gla.vdim});
+		m = std::max({m, l.mix.heads * l.mix.maps * l.mix.vdim, l.ssm.inner(), l.delta.heads * l.delta.vdim, l.mix.heads * l.latent.kv_rank, l.gla.heads * l.gla.vdim});
 	return m;
 }
 int StackSpec::max_proj() const {
@@ -174,9 +174,12 @@ int StackSpec::max_aux() const {
 
 int LayerSpec::proj_width() const {
 	if (kind == MixerKind::StateSpace) return ssm.proj();
-	if (kind == MixerKind::LatentAttention) return latent.q_rank + (latent.kv_from < 0 ? latent.kv_rank + latent.rot_dim : 0) + mix.heads * mix.vdim;
+	if (kind == MixerKind::LatentAttention) // [query latent, or the queries themselves | key / value latent + shared key part (own cache only) | gate]
+		return (latent.q_rank > 0 ? latent.q_rank : mix.heads * (mix.dim + latent.rot_dim)) + (latent.kv_from < 0 ? latent.kv_rank + latent.rot_dim : 0) +
+		       (mix.out_gate ? mix.heads * mix.vdim : 0);
 	if (kind == MixerKind::LinearAttention) return 2 * gla.heads * gla.dim + 2 * gla.heads * gla.vdim + gla.decay_rank;
-	int n = mix.heads * mix.dim + mix.kv_heads * mix.dim + (mix.values_are_keys ? 0 : mix.kv_heads * mix.vdim) + (mix.out_gate ? mix.heads * mix.vdim : 0);
+	int n = mix.maps * (mix.heads + mix.kv_heads) * mix.dim + (mix.values_are_keys ? 0 : mix.kv_heads * mix.vdim) + (mix.out_gate ? mix.heads * mix.vdim : 0);
+	if (mix.head_gate) n = (n + mix.heads + 3) & ~3; // one gate column per head; rows stay 16-byte multiples
 	if (kind == MixerKind::Parallel) n += 2 * delta.kv_heads * delta.dim + delta.heads * delta.vdim + delta.heads + delta.decay_rank + delta.gate_rank;
 	return n;
 }
@@ -663,10 +666,156 @@ int configure_fegizen(const JValue &j, Config &cfg) {
 	return 0;
 }
 
+// ---- Kiduvik ---------------------------------------------------------------------------------------------------------
+// A decoder-only stack with learned absolute positions and an RMS norm before AND after every sublayer,
+// x <- x + N_b(mixer(N_a(x))), x <- x + N_b(ff(N_a(x))); at the end of every layer a slice of a second token embedding,
+// gated by a projection of x, is projected back, normed and added.  Mixers: latent attention with full-rank queries (one cached
+// latent per position for keys and values, a shared rotated key part, half-split rotary pairs, causal, a stored sink per head in
+// the softmax's denominator; a layer may read another layer's cache) or differential attention (two softmax maps per head over
+// the same values, combined with a stored lambda; per-head RMS norm on q and k, YaRN-scaled half-split rotary positions on part
+// of each head, sliding window with kept first tokens, grouped key / value heads, per-head norm of the difference, one sigmoid
+// gate number per head).  Feed-forward: dense, not gated, with the exact GELU.
+std::string kiduvik_tensor(int layer, TensorRole role, int) {
+	const std::string l = "l" + std::to_string(layer) + ".", m = l + "mix.", f = l + "mlp.", sd = l + "side.";
+	switch (role) {
+	case TensorRole::Embed: return "embed";
+	case TensorRole::Positions: return "pos";
+	case TensorRole::SideEmbed: return "side.embed";
+	case TensorRole::FinalNorm: return "final.norm";
+	case TensorRole::Head: return "head";
+	case TensorRole::Norm1: return l + "norm1";
+	case TensorRole::Norm2: return l + "norm2";
+	case TensorRole::Norm1Post: return l + "norm1b";
+	case TensorRole::Norm2Post: return l + "norm2b";
+	case TensorRole::Wq: return m + "q";
+	case TensorRole::Wk: return m + "k";
+	case TensorRole::Wv: return m + "v";
+	case TensorRole::Wo: return m + "o";
+	case TensorRole::QNorm: return m + "q.norm";
+	case TensorRole::KNorm: return m + "k.norm";
+	case TensorRole::OutGate: return m + "g";
+	case TensorRole::DiffLq1: return m + "lq1";
+	case TensorRole::DiffLk1: return m + "lk1";
+	case TensorRole::DiffLq2: return m + "lq2";
+	case TensorRole::DiffLk2: return m + "lk2";
+	case TensorRole::LatentDkv: return m + "dkv";
+	case TensorRole::LatentDkvNorm: return m + "dkv.norm";
+	case TensorRole::LatentUk: return m + "uk";
+	case TensorRole::LatentUv: return m + "uv";
+	case TensorRole::Sink: return m + "sink";
+	case TensorRole::Up: return f + "up";
+	case TensorRole::Down: return f + "down";
+	case TensorRole::SideGate: return sd + "gate";
+	case TensorRole::SideProj: return sd + "proj";
+	case TensorRole::SideNorm: return sd + "norm";
+	default: break;
+	}
+	return "";
+}
+
+int fail_kiduvik(const char *what) {
+	fprintf(stderr, "yalm_b200: Kiduvik config.json: %s\n", what);
+	return YALM_EFORMAT;
+}
+
+// rot: {dims, base, scaling: {factor, original, fast, slow}} with half-split pairs
+int read_rotary(const JValue &r, int default_dims, RotarySpec *out) {
+	out->dims = r["dims"].integer(default_dims), out->base = r["base"].number(10000.0), out->interleaved = false;
+	const JValue &sc = r["scaling"];
+	if (sc.is_object()) {
+		out->factor = sc["factor"].number(0.0), out->original = sc["original"].number(0.0);
+		out->fast = sc["fast"].number(0.0), out->slow = sc["slow"].number(0.0);
+		if (!(out->factor > 0.0) || !(out->original > 0.0) || !(out->fast > 0.0) || !(out->slow > 0.0)) return 1;
+	}
+	return (out->dims < 0 || out->dims % 2 || !(out->base > 0.0)) ? 1 : 0;
+}
+
+int configure_kiduvik(const JValue &j, Config &cfg) {
+	auto spec = std::make_shared<StackSpec>();
+	StackSpec &s = *spec;
+	s.arch = "Kiduvik";
+	s.width = j["width"].integer(0);
+	s.vocab = j["vocab"].integer(0);
+	s.max_positions = j["max_positions"].integer(0);
+	s.norm_eps = (float)j["norm"]["eps"].number(1e-5);
+	s.learned_positions = true;
+	s.sandwich_norm = true;
+	s.token_side = j["token_side"].is_object() ? j["token_side"]["dim"].integer(0) : 0;
+	s.tensor_name = kiduvik_tensor;
+	if (s.width < 1 || s.vocab < 1 || s.max_positions < 1) return fail_kiduvik("width, vocab and max_positions must be positive");
+	if (s.token_side < 0) return fail_kiduvik("token_side.dim must be positive");
+	const JValue &layers = j["layers"];
+	if (!layers.is_array() || layers.arr.empty()) return fail_kiduvik("'layers' must be a non-empty list");
+	for (const JValue &jl : layers.arr) {
+		LayerSpec L;
+		const std::string type = jl["type"].string_or("");
+		const JValue &m = jl["mixer"];
+		const int li = (int)s.layers.size();
+		MixerSpec &x = L.mix;
+		x.heads = m["heads"].integer(0);
+		x.dim = m["dim"].integer(0), x.vdim = m["vdim"].integer(0);
+		x.scale = (float)m["scale"].number(1.0);
+		if (type == "latent_attention") {
+			L.kind = MixerKind::LatentAttention;
+			LatentSpec &y = L.latent;
+			x.kv_heads = 1; // every head reads the one cached row of a position
+			x.window = 0, x.sink = true;
+			y.q_rank = 0;
+			y.kv_rank = m["kv_rank"].integer(0), y.rot_dim = m["rot_dim"].integer(0);
+			y.kv_from = m["kv_from"].kind == JValue::Number ? m["kv_from"].integer(-1) : -1;
+			if (read_rotary(m["rot"], y.rot_dim, &y.rot)) return fail_kiduvik("bad rotary constants");
+			if (x.heads < 1 || x.dim < 0 || x.vdim < 1 || y.kv_rank < 1 || y.rot_dim < 0 || x.dim + y.rot_dim < 1) return fail_kiduvik("bad latent-attention sizes");
+			if (y.rot.dims > y.rot_dim) return fail_kiduvik("rot.dims must be even and at most rot_dim");
+			if (y.kv_from >= 0) {
+				if (y.kv_from >= li) return fail_kiduvik("kv_from must name an earlier layer");
+				const LayerSpec &o = s.layers[y.kv_from];
+				if (o.kind != MixerKind::LatentAttention || o.latent.kv_from >= 0 || o.latent.kv_rank != y.kv_rank || o.latent.rot_dim != y.rot_dim)
+					return fail_kiduvik("kv_from must name a latent-attention layer with its own cache and the same kv_rank and rot_dim");
+			}
+		} else if (type == "attention") {
+			L.kind = MixerKind::Attention;
+			x.kv_heads = m["kv_heads"].integer(x.heads);
+			x.maps = 2, x.diff = (float)m["diff"].number(0.0);
+			x.qk_norm = QkNorm::PerHead;
+			x.head_gate = true;
+			x.window = m["mask"]["size"].integer(0), x.keep_first = m["mask"]["keep_first"].integer(0);
+			if (read_rotary(m["rot"], 0, &x.rot)) return fail_kiduvik("bad rotary constants");
+			if (x.heads < 1 || x.kv_heads < 1 || x.heads % x.kv_heads || x.dim < 1 || x.vdim < 1 || x.window < 0 || x.keep_first < 0)
+				return fail_kiduvik("bad attention sizes");
+			if (x.rot.dims > x.dim) return fail_kiduvik("rot.dims must be even and at most dim");
+			if (x.window == 0) x.keep_first = 0; // no window: every earlier token is visible anyway
+		} else
+			return fail_kiduvik("unknown layer type (this build has: latent_attention, attention)");
+		const JValue &f = jl["mlp"];
+		if (f.is_object()) {
+			if (f["kind"].string_or("") != "dense") return fail_kiduvik("unknown mlp kind (this build has: dense)");
+			FfnSpec &F = L.ffn;
+			F.kind = FfnSpec::Dense, F.gated = false, F.act = GluAct::GeluErf;
+			F.ff = f["ff"].integer(0);
+			if (F.ff < 1) return fail_kiduvik("bad feed-forward size");
+		}
+		s.layers.push_back(L);
+	}
+	cfg.stack = spec;
+	cfg.dim = s.width;
+	cfg.vocab_size = s.vocab;
+	cfg.n_layers = (int)s.layers.size();
+	cfg.max_seq_len = s.max_positions;
+	cfg.norm_eps = s.norm_eps;
+	cfg.hidden_dim = std::max(1, s.max_ff());
+	cfg.n_heads = s.layers[0].mix.heads, cfg.n_kv_heads = s.layers[0].mix.kv_heads;
+	cfg.head_dim = 8;
+	while (cfg.n_heads * cfg.head_dim < std::max({s.max_aux(), s.max_o_dim(), s.max_proj()})) cfg.head_dim *= 2;
+	cfg.rotary_dim = 0;
+	cfg.n_experts = 0, cfg.n_experts_active = 0;
+	return 0;
+}
+
 const ArchEntry kArchs[] = {
     {"Retezen", configure_retezen},
     {"Fapudra", configure_fapudra},
     {"Fegizen", configure_fegizen},
+    {"Kiduvik", configure_kiduvik},
 };
 
 } // namespace

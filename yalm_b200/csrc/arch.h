@@ -16,9 +16,19 @@ struct Config;
 namespace yalm {
 
 // Normalisation of q and k before the scores.
-enum class QkNorm { None, WholeProjection /* RMS over all heads' channels at once, one weight per channel */ };
+enum class QkNorm {
+	None,
+	WholeProjection, /* RMS over all heads' channels at once, one weight per channel */
+	PerHead          /* RMS over each head's dim channels (each map's, with several maps), one weight of size dim shared by all heads */
+};
 // Gated feed-forward activations: y = act(g) * (u + up_offset), with optional clamps on g (from above) and u (both sides).
-enum class GluAct { Silu, Gelu /* tanh form, the reference's rounded constant */, SigmoidScaled /* g * sigmoid(alpha * g) */, GeluTanh /* tanh form, sqrt(2 / pi) to fp32 precision */ };
+enum class GluAct {
+	Silu,
+	Gelu /* tanh form, the reference's rounded constant */,
+	SigmoidScaled /* g * sigmoid(alpha * g) */,
+	GeluTanh /* tanh form, sqrt(2 / pi) to fp32 precision */,
+	GeluErf /* g Phi(g) with the exact error function */
+};
 // How router logits become expert scores.
 enum class RouterScore { Softmax, Sigmoid };
 // What a layer's token mixer is.
@@ -31,6 +41,20 @@ enum class MixerKind {
 };
 // How attention scores become weights.
 enum class AttnWeights { Softmax, Sigmoid /* sigmoid(score + head bias), not normalised over the keys */ };
+
+// Rotary positions: pair i of the first `dims` channels of a vector at position p turns by the angle p * f_i,
+// f_i = base^(-2 i / dims).  interleaved: pair i = channels (2 i, 2 i + 1); else (i, i + dims / 2).  factor > 0 rescales the
+// frequencies by wavelength (YaRN): with d(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(d(fast)), 0),
+// hi = min(ceil(d(slow)), dims - 1), r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1): f_i <- f_i / factor * r_i + f_i (1 - r_i),
+// and cos and sin are multiplied by 0.1 ln(factor) + 1.
+struct RotarySpec {
+	int dims = 0;
+	double base = 10000.0;
+	bool interleaved = true;
+	double factor = 0.0, original = 0.0, fast = 0.0, slow = 0.0;
+	// the table the kernels read: dims / 2 frequencies, and the factor on cos and sin (computed in double precision)
+	void table(std::vector<float> *freqs, float *magnitude) const;
+};
 
 struct MixerSpec {
 	int heads = 0, kv_heads = 0; // query head h reads key/value head h / (heads / kv_heads)
@@ -47,27 +71,21 @@ struct MixerSpec {
 	bool out_gate = false;       // heads * sigmoid(Wg input) before the output projection
 	int rel_rows = 0;            // > 0: a learned bias per (distance bucket, head) is added to the scaled score: distances below
 	int rel_far = 0;             // rel_rows / 2 have a row each, the rest are spaced logarithmically up to rel_far, then the last row
+	RotarySpec rot;              // dims > 0: rotary positions on the first dims channels of every query / key head (every map's)
+	int maps = 1;                // 2: differential attention.  q and k hold two maps per head, each an attention of its own over the same
+	                             // values; per head o = a_1 - lambda a_2, o / sqrt(mean o^2 + eps) (1 - diff), with
+	float diff = 0.f;            // lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff from four stored vectors of size dim
+	bool head_gate = false;      // every head's output times sigmoid(w_h . input), one number per head, before the output projection
+	bool sink = false;           // a stored number per head joins the softmax's denominator as exp(sink_h): no key, no value, not scaled
 };
 
-// Rotary positions: pair i of the first `dims` channels of a vector at position p turns by the angle p * f_i,
-// f_i = base^(-2 i / dims).  interleaved: pair i = channels (2 i, 2 i + 1); else (i, i + dims / 2).  factor > 0 rescales the
-// frequencies by wavelength (YaRN): with d(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(d(fast)), 0),
-// hi = min(ceil(d(slow)), dims - 1), r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1): f_i <- f_i / factor * r_i + f_i (1 - r_i),
-// and cos and sin are multiplied by 0.1 ln(factor) + 1.
-struct RotarySpec {
-	int dims = 0;
-	double base = 10000.0;
-	bool interleaved = true;
-	double factor = 0.0, original = 0.0, fast = 0.0, slow = 0.0;
-	// the table the kernels read: dims / 2 frequencies, and the factor on cos and sin (computed in double precision)
-	void table(std::vector<float> *freqs, float *magnitude) const;
-};
 
 // Latent attention: c_q = rms(W_dq x) w_q, q = W_uq c_q, per head [dim unrotated | rot_dim rotated]; W_dkv x = [kv_rank | rot_dim]:
 // the first part RMS-normed is the latent c, the rest, rotated, is one key part shared by all heads.  Per head the unrotated
 // key is W_uk c and the value W_uv c; score = (q_u . k_u + q_r . k_r) * scale.  The cache holds one row [c | k_r] per position,
 // and the products with W_uk and W_uv move to the query side: score = (W_uk^T q_u) . c + q_r . k_r, out = W_uv (sum_j p_j c_j).
 // kv_from >= 0: the layer has no W_dkv and reads that layer's cache rows with its own W_uk, W_uv, queries and window.
+// q_rank == 0: full-rank queries, q = W_q x.
 // heads, dim, vdim, scale, window and the output gate are MixerSpec's.
 struct LatentSpec {
 	int q_rank = 0, kv_rank = 0, rot_dim = 0, kv_from = -1;
@@ -121,6 +139,7 @@ struct FfnSpec {
 	float router_scale = 1.f;    // on the (renormalised) weights
 	int shared_ff = 0;           // > 0: one more gated feed-forward of this hidden size reads every row and is added
 	GluAct shared_act = GluAct::Silu;
+	bool gated = true;           // false: no gate matrix, y = W_down act(W_up h)
 };
 
 struct LayerSpec {
@@ -147,7 +166,8 @@ enum class TensorRole {
 	DeltaGate1, DeltaGate2, DeltaOut,
 	InConv1, InConv2, DepthWeights, RouterBias, SharedGate, SharedUp, SharedDown,
 	LatentDq, LatentDqNorm, LatentUq, LatentDkv, LatentDkvNorm, LatentUk, LatentUv,
-	GlaNorm, GlaDecay1, GlaDecay2, GlaDecayBias
+	GlaNorm, GlaDecay1, GlaDecay2, GlaDecayBias,
+	Norm1Post, Norm2Post, Sink, DiffLq1, DiffLk1, DiffLq2, DiffLk2, SideEmbed, SideGate, SideProj, SideNorm
 };
 
 struct StackSpec {
@@ -168,6 +188,9 @@ struct StackSpec {
 	bool layer_norm = false;       // norms subtract the mean: (x - mean) / sqrt(variance + eps) * w, no bias
 	int input_conv = 0;            // > 0: every sublayer reads h + conv(h), a causal convolution over time of this many taps on each
 	                               // channel of its normed input; the last taps - 1 normed inputs of both sublayers are sequence state
+	bool sandwich_norm = false;    // a norm before and after every sublayer: x += norm_b(sublayer(norm_a(x)))
+	int token_side = 0;            // > 0: at the end of layer i, with e = the layer's slice [i token_side, (i + 1) token_side) of a second
+	                               // embedding of the token: y = P (gelu_tanh(G x) * e), x += y / sqrt(mean y^2 + eps) * w (plain weight)
 	bool depth_average = false;    // what a layer hands on is a learned weighted sum of the embedding output and all layer results so far
 	// name of a tensor in the checkpoint; `expert` < 0 for tensors that are not per expert
 	std::string (*tensor_name)(int layer, TensorRole role, int expert) = nullptr;

@@ -260,7 +260,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
                                                                            const float *__restrict__ kp, const float *__restrict__ vp,
                                                                            float *__restrict__ part, int n_heads, int n_kv, int dk, int dv, int ring,
                                                                            int max_blocks, int window, int pool, float scale, int pos0,
-                                                                           const int *__restrict__ ctl, int ldk, int ldv) {
+                                                                           const int *__restrict__ ctl, int ldk, int ldv, const float *__restrict__ sink,
+                                                                           int v_heads) {
 	extern __shared__ __align__(16) float sm[];
 	const int dkp = (dk + 7) & ~7;
 	float *qs = sm;                                    // R x dkp
@@ -272,14 +273,15 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int i = first_pos(ctl, pos0) + m;
 	const int lo = window > 0 ? max(0, i - window + 1) : 0;
-	const int nb = (window > 0 && pool > 0 && i - window + 1 >= pool) ? (i - window + 1) / pool : 0;
+	const int nb = (window > 0 && pool > 0 && i - window + 1 >= pool) ? min((i - window + 1) / pool, max_blocks) : 0; // the pooled buffers hold max_blocks
 	for (int e = threadIdx.x; e < R * dkp; e += blockDim.x) {
 		const int r = e / dkp, d = e % dkp;
 		qs[e] = (r < nh && d < dk) ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
 	}
 	__syncthreads();
-	const CT *kbase = kc + (size_t)g * ring * ldk, *vbase = vc + (size_t)g * ring * ldv; // ldk, ldv: row strides of the rings (dk, dv when packed)
-	const float *kpb = kp ? kp + (size_t)g * max_blocks * dk : nullptr, *vpb = vp ? vp + (size_t)g * max_blocks * dv : nullptr;
+	const int gv = g % v_heads; // key heads beyond the value heads (further maps over the same values) wrap around
+	const CT *kbase = kc + (size_t)g * ring * ldk, *vbase = vc + (size_t)gv * ring * ldv; // ldk, ldv: row strides of the rings (dk, dv when packed)
+	const float *kpb = kp ? kp + (size_t)g * max_blocks * dk : nullptr, *vpb = vp ? vp + (size_t)gv * max_blocks * dv : nullptr;
 	const bool kvec_c = (dk * sizeof(CT)) % 16 == 0 && (ldk * sizeof(CT)) % 16 == 0 && aligned16(kbase), kvec_p = (dk * 4) % 16 == 0 && aligned16(kpb);
 	float mx[R], l[R], acc[R][DVC];
 #pragma unroll
@@ -362,7 +364,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_kernel(float
 			float o = 0.f;
 			for (int w = 0; w < kAttnWarps; ++w) o += wt[w] * macc[(w * R + r) * dv + c];
 			if (pr) pr[c] = o;
-			else out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+			else out[(size_t)m * ldo + (size_t)h * dv + c] = o * softmax_finish(M, L, sink, h);
 		}
 		if (pr && lane == 0) pr[dv] = M, pr[dv + 1] = L;
 	}
@@ -379,7 +381,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_lanes_kernel
                                                                                  const __nv_bfloat16 *__restrict__ vc, const float *__restrict__ kp,
                                                                                  const float *__restrict__ vp, float *__restrict__ part, int n_heads,
                                                                                  int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool,
-                                                                                 float scale, int pos0, const int *__restrict__ ctl) {
+                                                                                 float scale, int pos0, const int *__restrict__ ctl,
+                                                                                 const float *__restrict__ sink, int v_heads) {
 	extern __shared__ __align__(16) float sm[];
 	float *qs = sm;                                    // R x dk
 	float *macc = qs + R * dk;                         // kAttnWarps x R x dv
@@ -391,7 +394,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_lanes_kernel
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int i = first_pos(ctl, pos0) + m;
 	const int lo = window > 0 ? max(0, i - window + 1) : 0;
-	const int nb = (window > 0 && pool > 0 && i - window + 1 >= pool) ? (i - window + 1) / pool : 0;
+	const int nb = (window > 0 && pool > 0 && i - window + 1 >= pool) ? min((i - window + 1) / pool, max_blocks) : 0; // the pooled buffers hold max_blocks
 	for (int e = threadIdx.x; e < R * dk; e += blockDim.x) {
 		const int r = e / dk, d = e % dk;
 		qs[e] = r < nh ? q[(size_t)m * ldq + (size_t)(h0 + r) * dk + d] * scale : 0.f;
@@ -405,8 +408,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_lanes_kernel
 	for (int r = 0; r < R; ++r)
 #pragma unroll
 		for (int j = 0; j < 8; ++j) qr[r][j] = qs[r * dk + subk * 8 + j];
-	const __nv_bfloat16 *kbase = kc + (size_t)g * ring * dk + subk * 8, *vbase = vc + (size_t)g * ring * dv + subv * 8;
-	const float *kpb = kp ? kp + (size_t)g * max_blocks * dk + subk * 8 : nullptr, *vpb = vp ? vp + (size_t)g * max_blocks * dv + subv * 8 : nullptr;
+	const int gv = g % v_heads; // key heads beyond the value heads (further maps over the same values) wrap around
+	const __nv_bfloat16 *kbase = kc + (size_t)g * ring * dk + subk * 8, *vbase = vc + (size_t)gv * ring * dv + subv * 8;
+	const float *kpb = kp ? kp + (size_t)g * max_blocks * dk + subk * 8 : nullptr, *vpb = vp ? vp + (size_t)gv * max_blocks * dv + subv * 8 : nullptr;
 	float *scw = sc + warp * R * 32;
 	float mx[R], l[R], acc[R][8];
 #pragma unroll
@@ -534,14 +538,15 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_window_pool_lanes_kernel
 			float o = 0.f;
 			for (int w = 0; w < kAttnWarps; ++w) o += wt[w] * macc[(w * R + r) * dv + c];
 			if (pr) pr[c] = o;
-			else out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+			else out[(size_t)m * ldo + (size_t)h * dv + c] = o * softmax_finish(M, L, sink, h);
 		}
 		if (pr && lane == 0) pr[dv] = M, pr[dv + 1] = L;
 	}
 }
 
 // out[m, h, :] = sum_z w_z acc_z / sum_z w_z L_z with w_z = exp(M_z - max M), splits taken in order.  grid (heads, rows).
-__global__ void attn_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, int n_heads, int dv, int nsplit) {
+__global__ void attn_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, int n_heads, int dv, int nsplit,
+                                  const float *__restrict__ sink) {
 	const int h = blockIdx.x, m = blockIdx.y;
 	const float *pr = part + (size_t)(m * n_heads + h) * nsplit * (dv + 2);
 	float M = -INFINITY;
@@ -551,13 +556,14 @@ __global__ void attn_merge_kernel(float *__restrict__ out, int ldo, const float 
 		const float mz = pr[(size_t)z * (dv + 2) + dv];
 		if (mz != -INFINITY) L += expf(mz - M) * pr[(size_t)z * (dv + 2) + dv + 1];
 	}
+	const float fin = softmax_finish(M, L, sink, h);
 	for (int c = threadIdx.x; c < dv; c += blockDim.x) {
 		float o = 0.f;
 		for (int z = 0; z < nsplit; ++z) {
 			const float mz = pr[(size_t)z * (dv + 2) + dv];
 			if (mz != -INFINITY) o += expf(mz - M) * pr[(size_t)z * (dv + 2) + c];
 		}
-		out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+		out[(size_t)m * ldo + (size_t)h * dv + c] = o * fin;
 	}
 }
 
@@ -836,29 +842,29 @@ static bool attn_lanes_off() { // YALM_STACK_ATTN_LANES=0: A/B against the lane-
 template <int R>
 static int launch_attn_lanes(float *out, int ldo, const float *q, int ldq, const void *kr, const void *vr, const float *kp, const float *vp, float *ws,
                              int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool, float scale, int nsplit,
-                             int pos0, const int *ctl, cudaStream_t st) {
+                             int pos0, const int *ctl, const float *sink, int v_heads, cudaStream_t st) {
 	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
 	const size_t smem = sizeof(float) * ((size_t)R * dk + (size_t)kAttnWarps * R * dv + kAttnWarps * R * 2 + kAttnWarps * R * 32);
 	if (smem > 48 * 1024) return YALM_EINVAL;
 	attn_window_pool_lanes_kernel<R><<<dim3(n_kv * hg, n, nsplit), kAttnWarps * 32, smem, st>>>(
 	    out, ldo, q, ldq, (const __nv_bfloat16 *)kr, (const __nv_bfloat16 *)vr, kp, vp, nsplit > 1 ? ws : nullptr, n_heads, n_kv, dk, dv, ring, max_blocks,
-	    window, pool, scale, pos0, ctl);
-	if (nsplit > 1) attn_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit);
+	    window, pool, scale, pos0, ctl, sink, v_heads);
+	if (nsplit > 1) attn_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit, sink);
 	return (int)cudaGetLastError();
 }
 
 template <typename CT, int R, int DVC>
 static int launch_attn_wp(float *out, int ldo, const float *q, int ldq, const void *kr, const void *vr, const float *kp, const float *vp, float *ws,
                           int n, int n_heads, int n_kv, int dk, int dv, int ring, int max_blocks, int window, int pool, float scale, int nsplit,
-                          int pos0, const int *ctl, int ldk, int ldv, cudaStream_t st) {
+                          int pos0, const int *ctl, int ldk, int ldv, const float *sink, int v_heads, cudaStream_t st) {
 	const int rep = n_heads / n_kv, hg = (rep + R - 1) / R;
 	const size_t smem = sizeof(float) * ((size_t)R * ((dk + 7) & ~7) + (size_t)kAttnWarps * R * dv + kAttnWarps * R * 2);
 	if (smem > 160 * 1024) return YALM_EINVAL;
 	if (smem > 48 * 1024) YALM_TRY(cudaFuncSetAttribute(attn_window_pool_kernel<CT, R, DVC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	attn_window_pool_kernel<CT, R, DVC><<<dim3(n_kv * hg, n, nsplit), kAttnWarps * 32, smem, st>>>(
 	    out, ldo, q, ldq, (const CT *)kr, (const CT *)vr, kp, vp, nsplit > 1 ? ws : nullptr, n_heads, n_kv, dk, dv, ring, max_blocks, window, pool, scale,
-	    pos0, ctl, ldk, ldv);
-	if (nsplit > 1) attn_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit);
+	    pos0, ctl, ldk, ldv, sink, v_heads);
+	if (nsplit > 1) attn_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit, sink);
 	return (int)cudaGetLastError();
 }
 
@@ -877,8 +883,18 @@ extern "C" int yalm_attn_window_pool_strided(float *out, int ldo, const float *q
                                              const float *key_pool, const float *value_pool, float *workspace, int n, int n_heads, int n_kv, int dk, int dv,
                                              int ring, int max_blocks, int window, int pool, float scale, int cache_f32, int context, int pos0,
                                              const int *ctl, yalm_stream_t s) {
+	return yalm_attn_window_pool_sink(out, ldo, q, ldq, key_ring, ldk, value_ring, ldv, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring,
+	                                  max_blocks, window, pool, scale, cache_f32, context, pos0, ctl, nullptr, n_kv, s);
+}
+
+// The same with a sink per query head in the softmax's denominator (sink null: none) and with v_heads value heads for n_kv key
+// heads (key head g reads value head g % v_heads: several maps over the same values).
+extern "C" int yalm_attn_window_pool_sink(float *out, int ldo, const float *q, int ldq, const void *key_ring, int ldk, const void *value_ring, int ldv,
+                                          const float *key_pool, const float *value_pool, float *workspace, int n, int n_heads, int n_kv, int dk, int dv,
+                                          int ring, int max_blocks, int window, int pool, float scale, int cache_f32, int context, int pos0, const int *ctl,
+                                          const float *sink, int v_heads, yalm_stream_t s) {
 	if (!out || !q || !key_ring || !value_ring || n < 1 || n_kv < 1 || n_heads % n_kv || dv > 512 || ldk < dk || ldv < dv ||
-	    (pool > 0 && (!key_pool || !value_pool)))
+	    (pool > 0 && (!key_pool || !value_pool)) || v_heads < 1 || n_kv % v_heads)
 		return YALM_EINVAL;
 	cudaStream_t st = (cudaStream_t)s;
 	const int rep = n_heads / n_kv, R = rep >= 2 ? 4 : 1, hg = (rep + R - 1) / R;
@@ -898,7 +914,7 @@ extern "C" int yalm_attn_window_pool_strided(float *out, int ldo, const float *q
 		while (RL > 1 && (long)n_kv * ((rep + RL - 1) / RL) * n * nsplit < device_info().sms) RL >>= 1;
 #define LANES_CASE(R_)                                                                                                                \
 	return launch_attn_lanes<R_>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring, max_blocks, window, \
-	                             pool, scale, nsplit, pos0, ctl, st)
+	                             pool, scale, nsplit, pos0, ctl, sink, v_heads, st)
 		if (RL == 1) LANES_CASE(1);
 		if (RL == 2) LANES_CASE(2);
 		LANES_CASE(4);
@@ -906,7 +922,7 @@ extern "C" int yalm_attn_window_pool_strided(float *out, int ldo, const float *q
 	}
 #define ATTN_CASE(CT, R_, DVC_)                                                                                                       \
 	return launch_attn_wp<CT, R_, DVC_>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, workspace, n, n_heads, n_kv, dk, dv, ring, max_blocks, \
-	                                    window, pool, scale, nsplit, pos0, ctl, ldk, ldv, st)
+	                                    window, pool, scale, nsplit, pos0, ctl, ldk, ldv, sink, v_heads, st)
 #define ATTN_DVC(CT, R_)                                                                                                              \
 	if (dv <= 64) ATTN_CASE(CT, R_, 2);                                                                                               \
 	else if (dv <= 128) ATTN_CASE(CT, R_, 4);                                                                                         \

@@ -9,6 +9,7 @@
 // and the weights are fp32, the weights are rounded to bf16 only as the operand of P V.  Per row the mask is an interval
 // of the tile's key indices: blocks [0, nb(i)) or tokens [lo(i), i].
 #include "common.cuh"
+#include "stack_rows.cuh"
 
 #include <cuda_bf16.h>
 
@@ -44,7 +45,7 @@ __global__ void __launch_bounds__(128) attn_window_pool_mma_kernel(float *__rest
                                                                    const __nv_bfloat16 *__restrict__ kc, const __nv_bfloat16 *__restrict__ vc,
                                                                    const float *__restrict__ kp, const float *__restrict__ vp, int n, int n_heads, int n_kv,
                                                                    int ring, int max_blocks, int window, int pool, float scale, int pos0,
-                                                                   const int *__restrict__ ctl) {
+                                                                   const int *__restrict__ ctl, const float *__restrict__ sink, int v_heads) {
 	constexpr int LDK = DK + 8, LDV = DV + 8; // padded rows: 16 bytes of skew keep ldmatrix conflict-free
 	constexpr int KS = DK / 16;               // k-steps of Q K^T
 	constexpr int OT = DV / 8;                // 8-wide output tiles of P V
@@ -53,8 +54,9 @@ __global__ void __launch_bounds__(128) attn_window_pool_mma_kernel(float *__rest
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int h = blockIdx.y, g = h / (n_heads / n_kv), i0 = blockIdx.x * 64;
 	const int p0 = ctl ? ctl[CTL_POS] : pos0;
-	const __nv_bfloat16 *kbase = kc + (size_t)g * ring * DK, *vbase = vc + (size_t)g * ring * DV;
-	const float *kpb = kp ? kp + (size_t)g * max_blocks * DK : nullptr, *vpb = vp ? vp + (size_t)g * max_blocks * DV : nullptr;
+	const int gv = g % v_heads; // key heads beyond the value heads (further maps over the same values) wrap around
+	const __nv_bfloat16 *kbase = kc + (size_t)g * ring * DK, *vbase = vc + (size_t)gv * ring * DV;
+	const float *kpb = kp ? kp + (size_t)g * max_blocks * DK : nullptr, *vpb = vp ? vp + (size_t)gv * max_blocks * DV : nullptr;
 	// Q tile: fp32 -> bf16 (rows past n: zeros)
 	for (int c = threadIdx.x; c < 64 * (DK / 4); c += 128) {
 		const int r = c / (DK / 4), d = (c % (DK / 4)) * 4;
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(128) attn_window_pool_mma_kernel(float *__rest
 	const int iA = p0 + min(rA, n - 1), iB = p0 + min(rB, n - 1);
 	const int i_first = p0 + i0, i_last = p0 + min(i0 + 63, n - 1);
 	auto lo_of = [&](int i) { return window > 0 ? max(0, i - window + 1) : 0; };
-	auto nb_of = [&](int i) { return (window > 0 && pool > 0 && i - window + 1 >= pool) ? (i - window + 1) / pool : 0; };
+	auto nb_of = [&](int i) { return (window > 0 && pool > 0 && i - window + 1 >= pool) ? min((i - window + 1) / pool, max_blocks) : 0; };
 	const int loA = lo_of(iA), loB = lo_of(iB), nbA = nb_of(iA), nbB = nb_of(iB);
 	const int nb_max = nb_of(i_last), lo_min = lo_of(i_first);
 	const int pooled_tiles = (nb_max + 63) / 64, token_tiles = (i_last - lo_min) / 64 + 1;
@@ -199,17 +201,19 @@ __global__ void __launch_bounds__(128) attn_window_pool_mma_kernel(float *__rest
 	}
 	l0 += __shfl_xor_sync(kFull, l0, 1), l0 += __shfl_xor_sync(kFull, l0, 2);
 	l1 += __shfl_xor_sync(kFull, l1, 1), l1 += __shfl_xor_sync(kFull, l1, 2);
+	const float f0 = stack::softmax_finish(m0, l0, sink, h), f1 = stack::softmax_finish(m1, l1, sink, h);
 #pragma unroll
 	for (int t = 0; t < OT; ++t) {
 		const int d = h * DV + t * 8 + (lane & 3) * 2;
-		if (rA < n) *reinterpret_cast<float2 *>(out + (size_t)rA * ldo + d) = make_float2(o[t][0] / l0, o[t][1] / l0);
-		if (rB < n) *reinterpret_cast<float2 *>(out + (size_t)rB * ldo + d) = make_float2(o[t][2] / l1, o[t][3] / l1);
+		if (rA < n) *reinterpret_cast<float2 *>(out + (size_t)rA * ldo + d) = make_float2(o[t][0] * f0, o[t][1] * f0);
+		if (rB < n) *reinterpret_cast<float2 *>(out + (size_t)rB * ldo + d) = make_float2(o[t][2] * f1, o[t][3] * f1);
 	}
 }
 
 template <int DK, int DV>
 static int launch_mma(float *out, int ldo, const float *q, int ldq, const void *kr, const void *vr, const float *kp, const float *vp, int n, int n_heads,
-                      int n_kv, int ring, int max_blocks, int window, int pool, float scale, int pos0, const int *ctl, cudaStream_t st) {
+                      int n_kv, int ring, int max_blocks, int window, int pool, float scale, int pos0, const int *ctl, const float *sink, int v_heads,
+                      cudaStream_t st) {
 	const size_t smem = sizeof(__nv_bfloat16) * (3 * 64 * (DK + 8) + 2 * 64 * (DV + 8)); // Q, two key tiles, two value tiles
 	static bool configured = false;
 	if (!configured && smem > 48 * 1024) {
@@ -218,7 +222,7 @@ static int launch_mma(float *out, int ldo, const float *q, int ldq, const void *
 	}
 	attn_window_pool_mma_kernel<DK, DV><<<dim3((n + 63) / 64, n_heads), 128, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)kr, (const __nv_bfloat16 *)vr,
 	                                                                                   kp, vp, n, n_heads, n_kv, ring, max_blocks, window, pool, scale, pos0,
-	                                                                                   ctl);
+	                                                                                   ctl, sink, v_heads);
 	return (int)cudaGetLastError();
 }
 
@@ -424,6 +428,17 @@ extern "C" int yalm_attn_window_pool_mma_shape(int dk, int dv) {
 extern "C" int yalm_attn_window_pool_mma(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring,
                                          const float *key_pool, const float *value_pool, int n, int n_heads, int n_kv, int dk, int dv, int ring,
                                          int max_blocks, int window, int pool, float scale, int pos0, const int *ctl, yalm_stream_t s) {
+	return yalm_attn_window_pool_mma_sink(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, n, n_heads, n_kv, dk, dv, ring, max_blocks, window,
+	                                      pool, scale, pos0, ctl, nullptr, n_kv, s);
+}
+
+// The same with a sink per query head in the softmax's denominator (null: none) and v_heads value heads for n_kv key heads
+// (key head g reads value head g % v_heads).
+extern "C" int yalm_attn_window_pool_mma_sink(float *out, int ldo, const float *q, int ldq, const void *key_ring, const void *value_ring,
+                                              const float *key_pool, const float *value_pool, int n, int n_heads, int n_kv, int dk, int dv, int ring,
+                                              int max_blocks, int window, int pool, float scale, int pos0, const int *ctl, const float *sink, int v_heads,
+                                              yalm_stream_t s) {
+	if (v_heads < 1 || n_kv % v_heads) return YALM_EINVAL;
 	if (!out || !q || !key_ring || !value_ring || n < 1 || n_kv < 1 || n_heads % n_kv || (pool > 0 && (!key_pool || !value_pool)) || ldq % 4 || ldo % 2 ||
 	    ((uintptr_t)q & 15) || ((uintptr_t)out & 7) || !yalm_attn_window_pool_mma_shape(dk, dv))
 		return YALM_EINVAL;
@@ -431,7 +446,7 @@ extern "C" int yalm_attn_window_pool_mma(float *out, int ldo, const float *q, in
 #define MMA_CASE(DK_, DV_)                                                                                                            \
 	if (dk == DK_ && dv == DV_)                                                                                                       \
 	return launch_mma<DK_, DV_>(out, ldo, q, ldq, key_ring, value_ring, key_pool, value_pool, n, n_heads, n_kv, ring, max_blocks, window, pool, scale, pos0, \
-	                            ctl, st)
+	                            ctl, sink, v_heads, st)
 	MMA_CASE(64, 32);
 	MMA_CASE(64, 64);
 	MMA_CASE(64, 128);

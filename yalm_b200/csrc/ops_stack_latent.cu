@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(256) latent_post_rows_kernel(float *__restrict
 	__shared__ float red[33];
 	const int m = blockIdx.x, p = first_pos(ctl, pos0) + m;
 	float *row = P + (size_t)m * ld;
-	{
+	if (q_rank > 0) { // 0: the queries are projected at full rank, there is no query latent
 		float ss = 0.f;
 		for (int e = threadIdx.x; e < q_rank; e += blockDim.x) ss += row[o_q + e] * row[o_q + e];
 		ss = block_sum(ss, red);
@@ -418,7 +418,7 @@ template <int R, int NP>
 __global__ void __launch_bounds__(kLaWarps * 32) attn_latent_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
                                                                          const __nv_bfloat16 *__restrict__ rows, int ld, float *__restrict__ part,
                                                                          int n_heads, int dk, int dv, int ring, int window, float scale, int pos0,
-                                                                         const int *__restrict__ ctl) {
+                                                                         const int *__restrict__ ctl, const float *__restrict__ sink) {
 	extern __shared__ __align__(16) float sm[];
 	const int dkp = NP * 256;
 	float *qs = sm;                               // R x dkp, zero beyond dk
@@ -533,14 +533,15 @@ __global__ void __launch_bounds__(kLaWarps * 32) attn_latent_rows_kernel(float *
 			float o = 0.f;
 			for (int w2 = 0; w2 < kLaWarps; ++w2) o += wt[w2] * macc[(w2 * R + r) * dv + c];
 			if (pr) pr[c] = o;
-			else out[(size_t)m * ldo + (size_t)h * dv + c] = o / L;
+			else out[(size_t)m * ldo + (size_t)h * dv + c] = o * softmax_finish(M, L, sink, h);
 		}
 		if (pr && lane == 0) pr[dv] = M, pr[dv + 1] = L;
 	}
 }
 // out[m, h, :] = sum_z w_z acc_z / sum_z w_z L_z with w_z = exp(M_z - max M), splits taken in order (a split without keys has
 // M = -inf and no weight).  grid (heads, rows).
-__global__ void attn_latent_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, int n_heads, int dv, int nsplit) {
+__global__ void attn_latent_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, int n_heads, int dv, int nsplit,
+                                         const float *__restrict__ sink) {
 	__shared__ float wz[64]; // the splits' weights over the common sum (nsplit <= 64)
 	const int h = blockIdx.x, m = blockIdx.y;
 	const float *pr = part + (size_t)(m * n_heads + h) * nsplit * (dv + 2);
@@ -560,9 +561,10 @@ __global__ void attn_latent_merge_kernel(float *__restrict__ out, int ldo, const
 		// the sum runs over the splits in order
 		float L = 0.f;
 		for (int z = 0; z < nsplit; ++z) L += __shfl_sync(kFull, z < 32 ? e[0] * lz[0] : e[1] * lz[1], z & 31);
+		const float fin = softmax_finish(M, L, sink, h);
 #pragma unroll
 		for (int k = 0; k < 2; ++k)
-			if (lane + 32 * k < nsplit) wz[lane + 32 * k] = e[k] / L;
+			if (lane + 32 * k < nsplit) wz[lane + 32 * k] = e[k] * fin;
 	}
 	__syncthreads();
 	for (int c = threadIdx.x; c < dv; c += blockDim.x) {
@@ -641,7 +643,7 @@ extern "C" int yalm_add_norm_conv_rows(float *u, float *h, float *x, const float
 extern "C" int yalm_latent_post_rows(float *proj, int ld, int o_q, int q_rank, const float *q_norm, int o_kv, int kv_rank, int rot_dim, const float *kv_norm,
                                      void *ring_buf, int ring, const float *freq, float magnitude, int rot_dims, int interleaved, float eps, int cache_f32,
                                      int n, int pos0, const int *ctl, yalm_stream_t s) {
-	if (!proj || !q_norm || n < 1 || q_rank < 1 || rot_dims < 0 || rot_dims % 2 || rot_dims > rot_dim || (rot_dims > 0 && !freq) ||
+	if (!proj || n < 1 || q_rank < 0 || (q_rank > 0 && !q_norm) || rot_dims < 0 || rot_dims % 2 || rot_dims > rot_dim || (rot_dims > 0 && !freq) ||
 	    (ring_buf && (!kv_norm || kv_rank < 1 || ring < 1)))
 		return YALM_EINVAL;
 	cudaStream_t st = (cudaStream_t)s;
@@ -738,14 +740,14 @@ extern "C" int yalm_attn_latent_rows_shape(int dk, int dv, int ld) {
 
 template <int R, int NP>
 static int launch_attn_latent(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *ws, int n, int n_heads, int dk, int dv, int ring,
-                              int window, float scale, int nsplit, int pos0, const int *ctl, cudaStream_t st) {
+                              int window, float scale, int nsplit, int pos0, const int *ctl, const float *sink, cudaStream_t st) {
 	const size_t smem = sizeof(float) * ((size_t)R * NP * 256 + (size_t)kLaWarps * R * dv + kLaWarps * R * 2);
 	if (smem > 96 * 1024) return YALM_EINVAL;
 	if (smem > 48 * 1024) YALM_TRY(cudaFuncSetAttribute(attn_latent_rows_kernel<R, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 	attn_latent_rows_kernel<R, NP><<<dim3((n_heads + R - 1) / R, n, nsplit), kLaWarps * 32, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)rows, ld,
 	                                                                                                  nsplit > 1 ? ws : nullptr, n_heads, dk, dv, ring,
-	                                                                                                  window, scale, pos0, ctl);
-	if (nsplit > 1) attn_latent_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit);
+	                                                                                                  window, scale, pos0, ctl, sink);
+	if (nsplit > 1) attn_latent_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit, sink);
 	return (int)cudaGetLastError();
 }
 
@@ -754,6 +756,12 @@ static int launch_attn_latent(float *out, int ldo, const float *q, int ldq, cons
 // (split partials of calls with few rows), or null.
 extern "C" int yalm_attn_latent_rows(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *workspace, int n, int n_heads, int dk,
                                      int dv, int ring, int window, float scale, int context, int pos0, const int *ctl, yalm_stream_t s) {
+	return yalm_attn_latent_rows_sink(out, ldo, q, ldq, rows, ld, workspace, n, n_heads, dk, dv, ring, window, scale, context, pos0, ctl, nullptr, s);
+}
+
+// The same with a sink per head in the softmax's denominator (null: none).
+extern "C" int yalm_attn_latent_rows_sink(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *workspace, int n, int n_heads, int dk,
+                                          int dv, int ring, int window, float scale, int context, int pos0, const int *ctl, const float *sink, yalm_stream_t s) {
 	if (!out || !q || !rows || n < 1 || n_heads < 1 || ring < 1 || !yalm_attn_latent_rows_shape(dk, dv, ld) || ((uintptr_t)rows & 15)) return YALM_EINVAL;
 	const int R = n_heads >= 4 ? 4 : n_heads >= 2 ? 2 : 1, hg = (n_heads + R - 1) / R, NP = (dk / 8 + 31) / 32;
 	int nsplit = 1;
@@ -765,7 +773,7 @@ extern "C" int yalm_attn_latent_rows(float *out, int ldo, const float *q, int ld
 	}
 	cudaStream_t st = (cudaStream_t)s;
 #define LA_CASE(R_, NP_)                                                                                                              \
-	if (R == R_ && NP == NP_) return launch_attn_latent<R_, NP_>(out, ldo, q, ldq, rows, ld, workspace, n, n_heads, dk, dv, ring, window, scale, nsplit, pos0, ctl, st)
+	if (R == R_ && NP == NP_) return launch_attn_latent<R_, NP_>(out, ldo, q, ldq, rows, ld, workspace, n, n_heads, dk, dv, ring, window, scale, nsplit, pos0, ctl, sink, st)
 	LA_CASE(4, 1); LA_CASE(4, 2); LA_CASE(4, 3); LA_CASE(2, 1); LA_CASE(2, 2); LA_CASE(2, 3); LA_CASE(1, 1); LA_CASE(1, 2); LA_CASE(1, 3);
 #undef LA_CASE
 	return YALM_EINVAL;

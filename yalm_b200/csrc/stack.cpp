@@ -25,10 +25,18 @@
 #include <cstring>
 #include <iostream>
 
+// YALM_STACK_TRACE=1: a failing step names itself on stderr
+static bool st_trace() {
+	static const bool on = [] { const char *e = getenv("YALM_STACK_TRACE"); return e && e[0] == '1'; }();
+	return on;
+}
 #define ST_TRY(x)                                                                                                                  \
 	do {                                                                                                                           \
 		int rc__ = (int)(x);                                                                                                       \
-		if (rc__ != 0) return rc__;                                                                                                \
+		if (rc__ != 0) {                                                                                                           \
+			if (st_trace()) fprintf(stderr, "yalm_b200: %s:%d: %s -> %d\n", __FILE__, __LINE__, #x, rc__);                         \
+			return rc__;                                                                                                           \
+		}                                                                                                                          \
 	} while (0)
 
 namespace yalm {
@@ -83,6 +91,15 @@ struct StackLayer {
 	// experts: the choice bias; the shared expert
 	float *router_bias = nullptr;
 	void *wsgu = nullptr, *wsdown = nullptr;                  // (2 shared_ff, dim), (dim, shared_ff)
+	// ---- layers with a norm before and after every sublayer ----
+	bool sandwich = false;
+	float *norm1b = nullptr, *norm2b = nullptr;               // the norms on the sublayers' outputs
+	float *sink = nullptr;                                    // latent attention: one number per head in the softmax's denominator
+	// differential attention: columns [q: map, head | k: map, kv head | v | one gate number per head]; kring holds maps * kv heads key
+	// vectors per slot, vring kv heads; kpool / vpool (max_blocks = keep_first entries) the window's kept first tokens
+	float lambda = 0.f;
+	void *side_gate = nullptr, *side_proj = nullptr;          // token side input: (token_side, dim), (dim, token_side)
+	float *side_norm = nullptr;
 };
 
 } // namespace yalm
@@ -284,9 +301,65 @@ void Model::build_stack(YALMData &data) {
 	pl.push_back({&token_embedding_table, {mat(tensor(0, TensorRole::Embed, -1, {s.vocab, s.width}))}});
 	if (s.learned_positions) pl.push_back({&_pos_table, {mat(tensor(0, TensorRole::Positions, -1, {s.max_positions, s.width}))}});
 	pl.push_back({(void **)&rms_final_weight, {vec32(s.norm_scalar ? tensor(0, TensorRole::FinalNorm, -1, {}) : tensor(0, TensorRole::FinalNorm, -1, {s.width}))}});
+	if (s.token_side > 0) pl.push_back({&_side_table, {mat(tensor(0, TensorRole::SideEmbed, -1, {s.vocab, s.token_side * (int)s.layers.size()}))}});
 	if (s.depth_average) _scratch->hist_slabs = (int)s.layers.size() + 1;
 	if (s.embed_norm) pl.push_back({(void **)&_embed_norm, {vec32(s.norm_scalar ? tensor(0, TensorRole::EmbedNorm, -1, {}) : tensor(0, TensorRole::EmbedNorm, -1, {s.width}))}});
 	pl.push_back({&wcls, {mat(tensor(0, TensorRole::Head, -1, {s.vocab, s.width}))}});
+	// latent attention's tensors, rotary table and cache ring (layers with their own W_dkv); the packed projection's parts go to `proj`
+	auto load_latent = [&](int i, std::shared_ptr<StackLayer> &L, Placement &proj, int W) {
+		const yalm::LayerSpec &ls = L->spec;
+		const yalm::MixerSpec &m = ls.mix;
+		const yalm::LatentSpec &a = ls.latent;
+		const int no = m.heads * m.vdim, row = a.kv_rank + a.rot_dim;
+		const bool own = a.kv_from < 0;
+		const int nq = m.heads * (m.dim + a.rot_dim), qcols = a.q_rank > 0 ? a.q_rank : nq; // q_rank 0: the queries themselves
+		L->o_q = 0, L->o_kv = qcols, L->o_gate = qcols + (own ? row : 0);
+		L->kv_owner = own ? i : a.kv_from;
+		proj.parts.push_back(mat(a.q_rank > 0 ? tensor(i, TensorRole::LatentDq, -1, {a.q_rank, W}) : tensor(i, TensorRole::Wq, -1, {nq, W})));
+		if (own) proj.parts.push_back(mat(tensor(i, TensorRole::LatentDkv, -1, {row, W})));
+		if (m.out_gate) proj.parts.push_back(mat(tensor(i, TensorRole::OutGate, -1, {no, W})));
+		if (a.q_rank > 0) pl.push_back({(void **)&L->qnorm, {vec32(tensor(i, TensorRole::LatentDqNorm, -1, {a.q_rank}))}});
+		if (own) pl.push_back({(void **)&L->knorm, {vec32(tensor(i, TensorRole::LatentDkvNorm, -1, {a.kv_rank}))}});
+		if (a.q_rank > 0) pl.push_back({&L->wuq, {mat(tensor(i, TensorRole::LatentUq, -1, {nq, a.q_rank}))}});
+		if (m.sink) pl.push_back({(void **)&L->sink, {vec32(tensor(i, TensorRole::Sink, -1, {m.heads}))}});
+		// W_uk then W_uv in one piece: prompt portions multiply the cached latents by both at once
+		if (m.dim > 0)
+			pl.push_back({&L->wuk, {mat(tensor(i, TensorRole::LatentUk, -1, {m.heads * m.dim, a.kv_rank})), mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
+		else
+			pl.push_back({&L->wuv, {mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
+		if (m.dim > 0) { // the same matrix, each head transposed: an output channel of W_uk^T q is then one contiguous row
+			const auto uk = mat(tensor(i, TensorRole::LatentUk, -1, {m.heads * m.dim, a.kv_rank}));
+			const size_t es = dtype_size(dt);
+			_host_converted.emplace_back(uk.second);
+			char *t = _host_converted.back().data();
+			const char *src = static_cast<const char *>(uk.first);
+			for (int hh = 0; hh < m.heads; ++hh)
+				for (int d = 0; d < m.dim; ++d)
+					for (int cc = 0; cc < a.kv_rank; ++cc)
+						memcpy(t + (((size_t)hh * a.kv_rank + cc) * m.dim + d) * es, src + (((size_t)hh * m.dim + d) * a.kv_rank + cc) * es, es);
+			pl.push_back({&L->wukt, {{t, uk.second}}});
+		}
+		pl.push_back({&L->wo, {mat(tensor(i, TensorRole::Wo, -1, {W, no}))}});
+		if (a.rot.dims > 0) {
+			std::vector<float> fr;
+			a.rot.table(&fr, &L->rot_mag);
+			_host_converted.emplace_back(fr.size() * sizeof(float));
+			memcpy(_host_converted.back().data(), fr.data(), fr.size() * sizeof(float));
+			pl.push_back({(void **)&L->rot_freq, {{_host_converted.back().data(), fr.size() * sizeof(float)}}});
+		}
+		if (own) {
+			// one cache row [latent | rotated key part] per position; the ring covers the widest window of the layers that read it
+			int span = m.window;
+			bool unbounded = m.window == 0;
+			for (int k = i + 1; k < (int)s.layers.size(); ++k)
+				if (s.layers[k].kind == yalm::MixerKind::LatentAttention && s.layers[k].latent.kv_from == i)
+					span = std::max(span, s.layers[k].mix.window), unbounded = unbounded || s.layers[k].mix.window == 0;
+			L->ring = unbounded ? c.max_seq_len : std::min(c.max_seq_len, (span + c.stack_chunk + 63) / 64 * 64);
+			const size_t cb = c.weight_dtype == DType::F32 ? 4 : 2;
+			L->state_allocs.push_back({&L->kring, (size_t)L->ring * row * cb});
+		}
+		if (a.kv_rank > 512) die("latent attention: latents above 512 channels are not built");
+	};
 	bool have_first = false;
 	for (int i = 0; i < (int)s.layers.size(); ++i) {
 		auto L = std::make_shared<StackLayer>();
@@ -386,6 +459,86 @@ void Model::build_stack(YALMData &data) {
 			_stack.push_back(L);
 			continue;
 		}
+		if (s.sandwich_norm) {
+			// ---- a norm before and after each sublayer, one packed projection of the mixer's input, a plain feed-forward, the token side input ----
+			const int W = s.width;
+			const yalm::LayerSpec &ls = L->spec;
+			const FfnSpec &f = ls.ffn;
+			L->sandwich = true;
+			pl.push_back({(void **)&L->norm1, {vec32(tensor(i, TensorRole::Norm1, -1, {W}))}});
+			pl.push_back({(void **)&L->norm1b, {vec32(tensor(i, TensorRole::Norm1Post, -1, {W}))}});
+			Placement proj{&L->wproj, {}};
+			if (ls.kind == yalm::MixerKind::LatentAttention) {
+				load_latent(i, L, proj, W);
+			} else if (ls.kind == yalm::MixerKind::Attention && m.maps == 2) {
+				const int nq = m.maps * m.heads * m.dim, nk = m.maps * m.kv_heads * m.dim, nv = m.kv_heads * m.vdim, no = m.heads * m.vdim;
+				L->o_q = 0, L->o_k = nq, L->o_v = nq + nk, L->o_gate = nq + nk + nv;
+				// the checkpoint lays q and k out head by head as [map 1 | map 2]; the rows are reordered map by map, so that (map, head)
+				// is one list of attention heads over (map, kv head) key heads and kv heads value heads
+				auto by_map = [&](const Tensor *t, int heads) {
+					const auto src = mat(t);
+					const size_t rb = (size_t)W * dtype_size(dt) * m.dim; // bytes of one head's map
+					_host_converted.emplace_back(src.second);
+					char *dst = _host_converted.back().data();
+					for (int mp = 0; mp < m.maps; ++mp)
+						for (int hh = 0; hh < heads; ++hh)
+							memcpy(dst + ((size_t)mp * heads + hh) * rb, static_cast<const char *>(src.first) + ((size_t)hh * m.maps + mp) * rb, rb);
+					return std::make_pair((const void *)dst, src.second);
+				};
+				proj.parts.push_back(by_map(tensor(i, TensorRole::Wq, -1, {nq, W}), m.heads));
+				proj.parts.push_back(by_map(tensor(i, TensorRole::Wk, -1, {nk, W}), m.kv_heads));
+				proj.parts.push_back(mat(tensor(i, TensorRole::Wv, -1, {nv, W})));
+				if (m.head_gate) proj.parts.push_back(mat(tensor(i, TensorRole::OutGate, -1, {m.heads, W})));
+				if (m.qk_norm == yalm::QkNorm::PerHead) {
+					pl.push_back({(void **)&L->qnorm, {vec32(tensor(i, TensorRole::QNorm, -1, {m.dim}))}});
+					pl.push_back({(void **)&L->knorm, {vec32(tensor(i, TensorRole::KNorm, -1, {m.dim}))}});
+				}
+				{ // lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, one number for the layer, in fp32 as the rest of the combination
+					const float *v[4];
+					const TensorRole roles[4] = {TensorRole::DiffLq1, TensorRole::DiffLk1, TensorRole::DiffLq2, TensorRole::DiffLk2};
+					for (int k = 0; k < 4; ++k) v[k] = static_cast<const float *>(vec32(tensor(i, roles[k], -1, {m.dim})).first);
+					float d1 = 0.f, d2 = 0.f;
+					for (int d = 0; d < m.dim; ++d) d1 += v[0][d] * v[1][d], d2 += v[2][d] * v[3][d];
+					L->lambda = expf(d1) - expf(d2) + m.diff;
+				}
+				pl.push_back({&L->wo, {mat(tensor(i, TensorRole::Wo, -1, {W, no}))}});
+				if (m.rot.dims > 0) {
+					std::vector<float> fr;
+					m.rot.table(&fr, &L->rot_mag);
+					_host_converted.emplace_back(fr.size() * sizeof(float));
+					memcpy(_host_converted.back().data(), fr.data(), fr.size() * sizeof(float));
+					pl.push_back({(void **)&L->rot_freq, {{_host_converted.back().data(), fr.size() * sizeof(float)}}});
+				}
+				// rings for the window, fp32 buffers for the kept first tokens (read like pooled blocks of one token)
+				L->ring = m.window > 0 ? std::min(c.max_seq_len, (m.window + c.stack_chunk + 63) / 64 * 64) : c.max_seq_len;
+				const size_t cb = c.weight_dtype == DType::F32 ? 4 : 2;
+				L->state_allocs.push_back({&L->kring, (size_t)m.maps * m.kv_heads * L->ring * m.dim * cb});
+				L->state_allocs.push_back({&L->vring, (size_t)m.kv_heads * L->ring * m.vdim * cb});
+				L->max_blocks = m.window > 0 ? m.keep_first : 0;
+				if (L->max_blocks > 0) {
+					L->state_allocs.push_back({(void **)&L->kpool, (size_t)m.maps * m.kv_heads * L->max_blocks * m.dim * 4});
+					L->state_allocs.push_back({(void **)&L->vpool, (size_t)m.kv_heads * L->max_blocks * m.vdim * 4});
+				}
+				if (m.dim > 512 || m.vdim > 512) die("differential attention: head sizes above 512 are not built");
+			} else
+				die("layers with a norm on both sides take latent attention or differential attention");
+			pl.push_back(proj);
+			if (f.kind == FfnSpec::Dense) {
+				pl.push_back({(void **)&L->norm2, {vec32(tensor(i, TensorRole::Norm2, -1, {W}))}});
+				pl.push_back({(void **)&L->norm2b, {vec32(tensor(i, TensorRole::Norm2Post, -1, {W}))}});
+				if (f.gated) pl.push_back({&L->wgu, {mat(tensor(i, TensorRole::Gate, -1, {f.ff, W})), mat(tensor(i, TensorRole::Up, -1, {f.ff, W}))}});
+				else pl.push_back({&L->wgu, {mat(tensor(i, TensorRole::Up, -1, {f.ff, W}))}});
+				pl.push_back({&L->wdown, {mat(tensor(i, TensorRole::Down, -1, {W, f.ff}))}});
+			} else if (f.kind != FfnSpec::None)
+				die("layers with a norm on both sides take a dense feed-forward or none");
+			if (s.token_side > 0) {
+				pl.push_back({&L->side_gate, {mat(tensor(i, TensorRole::SideGate, -1, {s.token_side, W}))}});
+				pl.push_back({&L->side_proj, {mat(tensor(i, TensorRole::SideProj, -1, {W, s.token_side}))}});
+				pl.push_back({(void **)&L->side_norm, {vec32(tensor(i, TensorRole::SideNorm, -1, {W}))}});
+			}
+			_stack.push_back(L);
+			continue;
+		}
 		if (L->spec.kind == yalm::MixerKind::LatentAttention || L->spec.kind == yalm::MixerKind::LinearAttention) {
 			// ---- pre-norm layer: norm + input convolution per sublayer, one packed projection of the mixer's input, weighted sum over depth ----
 			const int W = s.width, taps = s.input_conv;
@@ -399,54 +552,7 @@ void Model::build_stack(YALMData &data) {
 			if (s.depth_average) pl.push_back({(void **)&L->depth_w, {vec32(tensor(i, TensorRole::DepthWeights, -1, {i + 2}))}});
 			Placement proj{&L->wproj, {}};
 			if (ls.kind == yalm::MixerKind::LatentAttention) {
-				const yalm::LatentSpec &a = ls.latent;
-				const int no = m.heads * m.vdim, row = a.kv_rank + a.rot_dim;
-				const bool own = a.kv_from < 0;
-				L->o_q = 0, L->o_kv = a.q_rank, L->o_gate = a.q_rank + (own ? row : 0);
-				L->kv_owner = own ? i : a.kv_from;
-				proj.parts.push_back(mat(tensor(i, TensorRole::LatentDq, -1, {a.q_rank, W})));
-				if (own) proj.parts.push_back(mat(tensor(i, TensorRole::LatentDkv, -1, {row, W})));
-				proj.parts.push_back(mat(tensor(i, TensorRole::OutGate, -1, {no, W})));
-				pl.push_back({(void **)&L->qnorm, {vec32(tensor(i, TensorRole::LatentDqNorm, -1, {a.q_rank}))}});
-				if (own) pl.push_back({(void **)&L->knorm, {vec32(tensor(i, TensorRole::LatentDkvNorm, -1, {a.kv_rank}))}});
-				pl.push_back({&L->wuq, {mat(tensor(i, TensorRole::LatentUq, -1, {m.heads * (m.dim + a.rot_dim), a.q_rank}))}});
-				// W_uk then W_uv in one piece: prompt portions multiply the cached latents by both at once
-				if (m.dim > 0)
-					pl.push_back({&L->wuk, {mat(tensor(i, TensorRole::LatentUk, -1, {m.heads * m.dim, a.kv_rank})), mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
-				else
-					pl.push_back({&L->wuv, {mat(tensor(i, TensorRole::LatentUv, -1, {no, a.kv_rank}))}});
-				if (m.dim > 0) { // the same matrix, each head transposed: an output channel of W_uk^T q is then one contiguous row
-					const auto uk = mat(tensor(i, TensorRole::LatentUk, -1, {m.heads * m.dim, a.kv_rank}));
-					const size_t es = dtype_size(dt);
-					_host_converted.emplace_back(uk.second);
-					char *t = _host_converted.back().data();
-					const char *src = static_cast<const char *>(uk.first);
-					for (int hh = 0; hh < m.heads; ++hh)
-						for (int d = 0; d < m.dim; ++d)
-							for (int cc = 0; cc < a.kv_rank; ++cc)
-								memcpy(t + (((size_t)hh * a.kv_rank + cc) * m.dim + d) * es, src + (((size_t)hh * m.dim + d) * a.kv_rank + cc) * es, es);
-					pl.push_back({&L->wukt, {{t, uk.second}}});
-				}
-				pl.push_back({&L->wo, {mat(tensor(i, TensorRole::Wo, -1, {W, no}))}});
-				if (a.rot.dims > 0) {
-					std::vector<float> fr;
-					a.rot.table(&fr, &L->rot_mag);
-					_host_converted.emplace_back(fr.size() * sizeof(float));
-					memcpy(_host_converted.back().data(), fr.data(), fr.size() * sizeof(float));
-					pl.push_back({(void **)&L->rot_freq, {{_host_converted.back().data(), fr.size() * sizeof(float)}}});
-				}
-				if (own) {
-					// one cache row [latent | rotated key part] per position; the ring covers the widest window of the layers that read it
-					int span = m.window;
-					bool unbounded = m.window == 0;
-					for (int k = i + 1; k < (int)s.layers.size(); ++k)
-						if (s.layers[k].kind == yalm::MixerKind::LatentAttention && s.layers[k].latent.kv_from == i)
-							span = std::max(span, s.layers[k].mix.window), unbounded = unbounded || s.layers[k].mix.window == 0;
-					L->ring = unbounded ? c.max_seq_len : std::min(c.max_seq_len, (span + c.stack_chunk + 63) / 64 * 64);
-					const size_t cb = c.weight_dtype == DType::F32 ? 4 : 2;
-					L->state_allocs.push_back({&L->kring, (size_t)L->ring * row * cb});
-				}
-				if (a.kv_rank > 512) die("latent attention: latents above 512 channels are not built");
+				load_latent(i, L, proj, W);
 			} else {
 				const yalm::GlaSpec &g = ls.gla;
 				const int hd = g.heads * g.dim, hp = g.heads * g.vdim;
@@ -541,7 +647,7 @@ void Model::build_stack(YALMData &data) {
 
 // layers whose cache and state are all in state_allocs (no key / value ring pair of the generic attention)
 static bool own_state(const StackLayer &L) {
-	return L.spec.kind == yalm::MixerKind::LatentAttention || L.spec.kind == yalm::MixerKind::LinearAttention;
+	return L.sandwich || L.spec.kind == yalm::MixerKind::LatentAttention || L.spec.kind == yalm::MixerKind::LinearAttention;
 }
 
 void Model::cuda_stack(int device) {
@@ -616,8 +722,9 @@ void Model::cuda_stack(int device) {
 		const yalm::LayerSpec &ls = L->spec;
 		if (ls.kind != yalm::MixerKind::LatentAttention) continue;
 		if (ls.mix.dim > 0 && !L->wuv) L->wuv = static_cast<char *>(L->wuk) + (size_t)ls.mix.heads * ls.mix.dim * ls.latent.kv_rank * dtype_size(c.weight_dtype);
-		if (c.weight_dtype == DType::F32 || ls.mix.window < 1) continue;
-		const size_t rows = std::min<size_t>(L->ring, (size_t)ls.mix.window + c.stack_chunk), H = ls.mix.heads;
+		if (c.weight_dtype == DType::F32 || (ls.mix.window < 1 && !L->sandwich)) continue;
+		// the rows a portion sees: the window before it and itself, or (no window) everything the ring holds
+		const size_t rows = ls.mix.window > 0 ? std::min<size_t>(L->ring, (size_t)ls.mix.window + c.stack_chunk) : (size_t)L->ring, H = ls.mix.heads;
 		lat16 = std::max(lat16, rows * ls.latent.kv_rank * 2), latkv = std::max(latkv, rows * H * (ls.mix.dim + ls.mix.vdim) * 4);
 		lat_ek = std::max(lat_ek, H * L->ring * (ls.mix.dim + ls.latent.rot_dim) * 2), lat_ev = std::max(lat_ev, H * L->ring * ls.mix.vdim * 2);
 	}
@@ -987,6 +1094,109 @@ int Model::stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int i
 	return yalm_residual_sum_rows(S.x, add_a, add_b, slots, W, nsum, n, W, st);
 }
 
+static int plain_act_code(yalm::GluAct a) {
+	return a == yalm::GluAct::GeluErf ? 4 : a == yalm::GluAct::GeluTanh ? 3 : a == yalm::GluAct::Silu ? YALM_ACT_SILU : YALM_ACT_GELU;
+}
+
+// One layer with a norm on both sides of each sublayer over n rows: x += N1b(mixer(N1(x))), x += N2b(ff(N2(x))), then the token
+// side input.  The mixer is latent attention with full-rank queries and a sink per head over cached rows [latent | rotated key
+// part] (its own, or another layer's), or differential attention: (map, head) is one list of attention heads over rings that
+// hold (map, kv head) key vectors and kv heads values, the window's kept first tokens are read like pooled blocks of one token,
+// and the two maps of a head are combined afterwards.  What the rows leave for the next call is written by the ops themselves.
+int Model::stack_layer_sandwich(StackScratch &S, const yalm::StackLayer &L, int index, int n, int pos0, const int *ctl, bool from_ctl, cudaStream_t st) {
+	const Config &c = *config;
+	const StackSpec &sp = *c.stack;
+	const yalm::LayerSpec &ls = L.spec;
+	const yalm::MixerSpec &m = ls.mix;
+	const int dt = static_cast<int>(c.weight_dtype), W = sp.width, f32 = c.weight_dtype == DType::F32;
+	const int ldp = ls.proj_width(), no = m.heads * m.vdim;
+	float *P = S.qkv;
+	// ---- token mixer ----
+	ST_TRY(yalm_norm_shift_rows(S.xn, nullptr, S.x, L.norm1, 0, 0.f, sp.norm_eps, nullptr, nullptr, n, W, pos0, ctl, st));
+	if (ls.kind == yalm::MixerKind::LatentAttention) {
+		const yalm::LatentSpec &a = ls.latent;
+		const int row = a.kv_rank + a.rot_dim, nqa = m.heads * row, nl = m.heads * a.kv_rank, dk = m.dim + a.rot_dim;
+		const bool own = a.kv_from < 0;
+		ST_TRY(stack_linear(*this, c, S.a16, P, ldp, S.xn, W, L.wproj, n, ldp, W, 1.f, st));
+		if (own)
+			ST_TRY(yalm_latent_post_rows(P, ldp, L.o_q, 0, nullptr, L.o_kv, a.kv_rank, a.rot_dim, L.knorm, L.kring, L.ring, L.rot_freq, L.rot_mag, a.rot.dims,
+			                             a.rot.interleaved ? 1 : 0, sp.norm_eps, f32, n, pos0, ctl, st));
+		float *Q = P + L.o_q; // the queries as projected, per head [unrotated | rotated part]
+		if (!f32 && !ctl && n >= 16 && m.dim > 0 && S.lat16 && a.kv_rank % 8 == 0 && ldp % 4 == 0 && no % 2 == 0 && (m.heads * (m.dim + m.vdim)) % 4 == 0 &&
+		    yalm_attn_window_pool_mma_shape(dk, m.vdim) && !attn_mma_off()) {
+			// A prompt portion in 16-bit: the latents of the visible rows times [W_uk ; W_uv] on the tensor cores give every head's keys
+			// and values, written beside the rotated key part into head-major rings for the tensor-core attention.
+			const int first = m.window > 0 ? std::max(0, pos0 - m.window + 1) : 0, count = pos0 + n - first, nkv = m.heads * (m.dim + m.vdim);
+			ST_TRY(yalm_latent_gather_rows16(S.lat16, L.kring, L.ring, row, a.kv_rank, first, count, st));
+			ST_TRY(yalm_gemm_16(S.latkv, nkv, S.lat16, L.wuk, count, nkv, a.kv_rank, 0, dt == YALM_BF16, 1.f, st));
+			ST_TRY(yalm_latent_pack_rings(S.lat_ek, S.lat_ev, S.latkv, nkv, L.kring, L.ring, a.kv_rank, a.rot_dim, m.heads, m.dim, m.vdim, L.ring, first, count, st));
+			ST_TRY(yalm_rotate_heads_rows(Q, ldp, m.heads, dk, m.dim, L.rot_freq, L.rot_mag, a.rot.dims, a.rot.interleaved ? 1 : 0, n, pos0, ctl, st));
+			ST_TRY(yalm_attn_window_pool_mma_sink(S.att, no, Q, ldp, S.lat_ek, S.lat_ev, nullptr, nullptr, n, m.heads, m.heads, dk, m.vdim, L.ring, 0, m.window, 0,
+			                                      m.scale, pos0, ctl, L.sink, m.heads, st));
+		} else {
+			// A decode row (and what the tensor-core route does not take): W_uk moves to the query side, every head reads the one cached
+			// row of a position — keys are whole rows, values their first kv_rank channels — and W_uv follows the weighted sum.
+			ST_TRY(yalm_latent_query_rows(S.aux, nqa, Q, ldp, L.wukt, dt, n, m.heads, m.dim, a.rot_dim, a.kv_rank, L.rot_freq, L.rot_mag, a.rot.dims,
+			                              a.rot.interleaved ? 1 : 0, pos0, ctl, st));
+			if (!f32 && yalm_attn_latent_rows_shape(row, a.kv_rank, row) && ((uintptr_t)L.kring & 15) == 0 && nqa % 4 == 0)
+				ST_TRY(yalm_attn_latent_rows_sink(S.scan, nl, S.aux, nqa, L.kring, row, S.attn_ws, n, m.heads, row, a.kv_rank, L.ring, m.window, m.scale,
+				                                  c.max_seq_len, pos0, ctl, L.sink, st));
+			else
+				ST_TRY(yalm_attn_window_pool_sink(S.scan, nl, S.aux, nqa, L.kring, row, L.kring, row, nullptr, nullptr, S.attn_ws, n, m.heads, 1, row, a.kv_rank,
+				                                  L.ring, 0, m.window, 0, m.scale, f32, c.max_seq_len, pos0, ctl, L.sink, 1, st));
+			ST_TRY(yalm_head_linear_gate_rows(S.att, no, S.scan, nl, L.wuv, dt, nullptr, 0, n, m.heads, m.vdim, a.kv_rank, st));
+		}
+	} else {
+		const int nqv = m.maps * m.heads, nkv = m.maps * m.kv_heads, ncols = L.o_gate + (m.head_gate ? m.heads : 0), na = m.maps * no;
+		const int keep = L.max_blocks, pool = keep > 0 ? 1 : 0;
+		ST_TRY(stack_linear(*this, c, S.a16, P, ldp, S.xn, W, L.wproj, n, ncols, W, 1.f, st));
+		ST_TRY(yalm_head_norm_rope_append_rows(P, ldp, L.o_q, L.o_k, L.o_v, nqv, nkv, m.kv_heads, m.dim, m.vdim, L.qnorm, L.knorm, L.rot_freq, L.rot_mag,
+		                                       m.rot.dims, m.rot.interleaved ? 1 : 0, sp.norm_eps, L.kring, L.vring, L.ring, L.kpool, L.vpool, keep, f32, n, pos0,
+		                                       ctl, st));
+		// many rows over bf16 rings: tensor-core attention; decode-sized calls, the fp32 cache and other head sizes: the SIMT kernels
+		if (!f32 && n >= 16 && ldp % 4 == 0 && na % 2 == 0 && yalm_attn_window_pool_mma_shape(m.dim, m.vdim) && !attn_mma_off())
+			ST_TRY(yalm_attn_window_pool_mma_sink(S.scan, na, P + L.o_q, ldp, L.kring, L.vring, L.kpool, L.vpool, n, nqv, nkv, m.dim, m.vdim, L.ring, keep, m.window,
+			                                      pool, m.scale, pos0, ctl, nullptr, m.kv_heads, st));
+		else
+			ST_TRY(yalm_attn_window_pool_sink(S.scan, na, P + L.o_q, ldp, L.kring, m.dim, L.vring, m.vdim, L.kpool, L.vpool, S.attn_ws, n, nqv, nkv, m.dim, m.vdim,
+			                                  L.ring, keep, m.window, pool, m.scale, f32, c.max_seq_len, pos0, ctl, nullptr, m.kv_heads, st));
+		ST_TRY(yalm_diff_combine_rows(S.att, no, S.scan, na, m.head_gate ? P + L.o_gate : nullptr, ldp, n, m.heads, m.vdim, L.lambda, 1.f - m.diff, sp.norm_eps, st));
+	}
+	// output projection, the norm on its result and the residual add: one launch for a decode row
+	if (gemv_fusable(c, n, no, L.wo, S.att))
+		ST_TRY(yalm_gemv_norm_residual(S.x, S.y1, S.att, L.wo, L.norm1b, 0.f, sp.norm_eps, no, W, dt, 0, 0, 0.f, 0.f, 0.f, S.ticket, st));
+	else {
+		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, no, L.wo, n, W, no, 1.f, st));
+		ST_TRY(yalm_norm_residual_rows(S.x, S.y1, W, 1, L.norm1b, 0.f, sp.norm_eps, n, W, st));
+	}
+	// ---- feed-forward ----
+	const FfnSpec &f = ls.ffn;
+	if (f.kind == FfnSpec::Dense) {
+		ST_TRY(yalm_norm_shift_rows(S.xn, nullptr, S.x, L.norm2, 0, 0.f, sp.norm_eps, nullptr, nullptr, n, W, pos0, ctl, st));
+		const float *hid;
+		if (f.gated) {
+			ST_TRY(stack_linear(*this, c, S.a16, S.gu, 2 * f.ff, S.xn, W, L.wgu, n, 2 * f.ff, W, 1.f, st));
+			ST_TRY(yalm_glu_act_rows(S.h, S.gu, n, f.ff, glu_act_code(f.act), f.act_alpha, f.limit, f.up_offset, st));
+			hid = S.h;
+		} else {
+			ST_TRY(stack_linear(*this, c, S.a16, S.gu, f.ff, S.xn, W, L.wgu, n, f.ff, W, 1.f, st));
+			ST_TRY(yalm_act_rows(S.gu, f.ff, n, f.ff, plain_act_code(f.act), st));
+			hid = S.gu;
+		}
+		if (gemv_fusable(c, n, f.ff, L.wdown, hid))
+			ST_TRY(yalm_gemv_norm_residual(S.x, S.y1, hid, L.wdown, L.norm2b, 0.f, sp.norm_eps, f.ff, W, dt, 0, 0, 0.f, 0.f, 0.f, S.ticket, st));
+		else {
+			ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, hid, f.ff, L.wdown, n, W, f.ff, 1.f, st));
+			ST_TRY(yalm_norm_residual_rows(S.x, S.y1, W, 1, L.norm2b, 0.f, sp.norm_eps, n, W, st));
+		}
+	}
+	// ---- token side input ----
+	if (sp.token_side > 0)
+		ST_TRY(yalm_token_side_rows(S.x, _side_table, sp.token_side * (int)sp.layers.size(), index * sp.token_side, from_ctl ? nullptr : S.tokens, ctl, L.side_gate,
+		                            L.side_proj, L.side_norm, dt, n, W, sp.token_side, sp.norm_eps, st));
+	return 0;
+}
+
 int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_want) {
 	const Config &c = *config;
 	const StackSpec &sp = *c.stack;
@@ -1011,6 +1221,11 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 		const StackLayer &L = *Lp;
 		if (sp.parallel_block) {
 			ST_TRY(stack_layer_parallel(S, L, n, pos0, ctl, st));
+			ST_TRY(tap());
+			continue;
+		}
+		if (L.sandwich) {
+			ST_TRY(stack_layer_sandwich(S, L, layer_no, n, pos0, ctl, from_ctl, st));
 			ST_TRY(tap());
 			continue;
 		}

@@ -57,6 +57,14 @@ __device__ __forceinline__ void cache_put(__nv_bfloat16 *p, size_t i, float v) {
 
 __device__ __forceinline__ int first_pos(const int *ctl, int pos0) { return ctl ? ctl[CTL_POS] : pos0; }
 
+// A sink joins the softmax's denominator as exp(sink) without a key or a value: the factor on an accumulator whose weights
+// are exp(score - M) and sum to L is 1 / (L + exp(sink - M)), formed over the larger of M and the sink so that nothing overflows.
+__device__ __forceinline__ float softmax_finish(float M, float L, const float *sink, int h) {
+	if (!sink) return 1.0f / L;
+	const float sk = sink[h], top = fmaxf(M, sk), f = expf(M - top);
+	return f / (L * f + expf(sk - top));
+}
+
 __host__ __device__ inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 // dot(weight row, x) over K elements, result in every lane.  `vec`: the row and x are 16-byte aligned and K % VEC == 0.

@@ -325,6 +325,7 @@ private:
 	std::vector<std::shared_ptr<yalm::StackLayer>> _stack;
 	float *_embed_norm = nullptr;                   // weight of the norm after the embedding, when the design has one
 	void *_pos_table = nullptr;                     // learned positions (max_positions, dim), weight dtype
+	void *_side_table = nullptr;                    // second token embedding (vocab, layers * token_side), weight dtype
 	std::vector<std::vector<char>> _host_converted; // weights converted on the host (bf16 -> fp32, norm weights), alive until the upload
 	struct StackScratch;
 	std::shared_ptr<StackScratch> _scratch;
@@ -339,6 +340,7 @@ private:
 	int stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const float *x, void *a16, int n, int act, cudaStream_t st);
 	int stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int n, int pos0, const int *ctl, cudaStream_t st);
 	int stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int index, int n, int pos0, const int *ctl, cudaStream_t st);
+	int stack_layer_sandwich(StackScratch &S, const yalm::StackLayer &L, int index, int n, int pos0, const int *ctl, bool from_ctl, cudaStream_t st);
 	int stack_generate(InferenceState &s, int token, int pos, int n_gen, float temperature, unsigned long long seed, int *tokens_out,
 	                   float *logits_out, float *device_ms);
 	Device _device = Device::CPU;
