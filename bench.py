@@ -49,6 +49,7 @@ WORKLOADS = {
     "retezen-sizes": ("tiny", "bf16", 4096, "Retezen (windowed attention with pooled blocks, dense / routed feed-forward) at model-like sizes"),
     "fapudra-sizes": ("tiny", "bf16", 4096, "Fapudra (parallel blocks: state-space / sigmoid attention + gated delta rule, routed experts) at model-like sizes"),
     "fegizen-sizes": ("tiny", "bf16", 4096, "Fegizen (latent attention over cached latents / gated linear attention, experts with identity and shared experts) at model-like sizes"),
+    "kiduvik-sizes": ("tiny", "bf16", 4096, "Kiduvik (latent attention with a sink over cached latents / differential attention over a window with kept first tokens, dense feed-forward, token side input) at model-like sizes"),
     "mistral-7b-fp16-prefill": ("mistral-7b", "fp16", 4096, "Mistral-7B-v0.2 fp16 random-init, 4096-token prompt hydrated in 512-token chunks (tcgen05 GEMMs)"),
 }
 HEADLINE = "mistral-7b-fp16-4k"
@@ -374,6 +375,11 @@ def main():
             raise SystemExit("bench.py: the layered models run on one GPU")
         from yalm_b200 import stack_bench
         return stack_bench.run_fegizen(args, base, _emit, shm_path, ClockSampler)
+    if args.workload == "kiduvik-sizes":
+        if world > 1:
+            raise SystemExit("bench.py: the layered models run on one GPU")
+        from yalm_b200 import stack_bench
+        return stack_bench.run_kiduvik(args, base, _emit, shm_path, ClockSampler)
     if args.workload.endswith("-prefill"):
         if world > 1:
             raise SystemExit("bench.py: the prefill workload is single-GPU")

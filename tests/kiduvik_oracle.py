@@ -295,6 +295,8 @@ def write_checkpoint(folder, cfg, w):
         json.dump(cfg, f)
     header, blobs, at = {}, [], 0
     for name, a in w.items():
+        if np.size(a) == 0:      # a head part of size zero has no tensor
+            continue
         b = (np.asarray(a, dtype=np.float32).view(np.uint32) >> 16).astype("<u2").tobytes()
         header[name] = {"dtype": "BF16", "shape": list(np.shape(a)), "data_offsets": [at, at + len(b)]}
         blobs.append(b)

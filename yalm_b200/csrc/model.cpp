@@ -118,6 +118,23 @@ size_t Config::active_bytes(size_t pos) const {
 				if (l.ffn.kind == yalm::FfnSpec::Moe) total += ((size_t)l.ffn.experts * W + (size_t)l.ffn.top * 3 * l.ffn.ff * W) * ws;
 				continue;
 			}
+			if (s.sandwich_norm) {
+				// four norm weights; the packed projection and the output projection; latent attention: the per-head maps and one cached row
+				// per position for all heads (no row of its own when it reads another layer's; the rows are still read); differential
+				// attention: the window of keys (both maps) and values plus the kept first tokens; the feed-forward; the side input
+				total += ((size_t)l.proj_width() + (size_t)m.heads * m.vdim) * W * ws + 4 * W * 4;
+				if (l.kind == yalm::MixerKind::LatentAttention) {
+					const yalm::LatentSpec &a = l.latent;
+					total += (size_t)m.heads * (m.dim + m.vdim) * a.kv_rank * ws + (pos + 1) * (a.kv_rank + a.rot_dim) * cb;
+				} else {
+					const size_t seen = m.window > 0 ? std::min<size_t>(pos + 1, m.window) : pos + 1;
+					const size_t kept = m.window > 0 && pos + 1 > (size_t)m.window ? std::min<size_t>(m.keep_first, pos + 1 - m.window) : 0;
+					total += (seen * cb + kept * 4) * ((size_t)m.maps * m.kv_heads * m.dim + (size_t)m.kv_heads * m.vdim);
+				}
+				if (l.ffn.kind == yalm::FfnSpec::Dense) total += (size_t)(l.ffn.gated ? 3 : 2) * l.ffn.ff * W * ws;
+				if (s.token_side > 0) total += ((size_t)2 * s.token_side * W + s.token_side) * ws + W * 4;
+				continue;
+			}
 			if (l.kind == yalm::MixerKind::LatentAttention || l.kind == yalm::MixerKind::LinearAttention) {
 				// the packed projection and the output projection, the per-head maps, the window of cached rows (one row per position for
 				// all heads) or the fp32 matrix state read and written; the chosen experts, the router and the shared expert
@@ -848,7 +865,9 @@ int Model::launches_per_forward(InferenceMode mode) const {
 	if (config->stack) { // before any capture, the per-op route: embed + per layer: qkv, q/k norm + append, [pool], attention, wo, norm + residual, feed-forward (4) [+ final norm, head]
 		int n = 1;
 		for (const yalm::LayerSpec &l : config->stack->layers) {
-			if (config->stack->parallel_block) // norm + shift, projection, mixer (state space 5, parallel 14), experts 3, residual
+			if (config->stack->sandwich_norm) // norm, projection, mixer (latent 5 with the split merge, differential 4), output projection + norm; norm, up, activation, down + norm; side input
+				n += 2 + (l.kind == yalm::MixerKind::LatentAttention ? 5 : 4) + 1 + (l.ffn.kind == yalm::FfnSpec::None ? 0 : 4) + (config->stack->token_side > 0 ? 1 : 0);
+			else if (config->stack->parallel_block) // norm + shift, projection, mixer (state space 5, parallel 14), experts 3, residual
 				n += 3 + (l.kind == yalm::MixerKind::StateSpace ? 5 : 14) + (l.ffn.kind == yalm::FfnSpec::None ? 0 : 3);
 			else if (l.kind == yalm::MixerKind::LatentAttention || l.kind == yalm::MixerKind::LinearAttention) // norm + conv, projection, mixer (8 / 5), norm + conv, feed-forward (3, or 3 + 3 with a shared expert), depth sum
 				n += 2 + (l.kind == yalm::MixerKind::LatentAttention ? 8 : 5) + 1 +

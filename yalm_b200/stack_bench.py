@@ -419,6 +419,167 @@ def run_fegizen(args, base, emit, shm_path, ClockSampler):
                           l2="inputs larger than L2 (weights streamed per token)")))
 
 
+# ---- Kiduvik ---------------------------------------------------------------------------------------------------------------
+# name: width; latent attention heads x (dim unrotated + rot rotated), values, latent size; differential attention heads / kv heads of
+# dim per map, values, window, kept first tokens; feed-forward (not gated), token side size; layer order (l = latent attention with its
+# own cache, s = latent attention on the first l's cache, d = differential attention)
+KIDUVIK_SIZES = {
+    "w2048": dict(width=2048, heads=16, dim=64, rot=64, vdim=128, kv_rank=512, dheads=16, dkv=4, ddim=64, dvdim=128, window=1024, keep=4, ff=8192, side=64,
+                  order="lsdl", vocab=32000),
+    "w4096": dict(width=4096, heads=32, dim=64, rot=64, vdim=128, kv_rank=512, dheads=32, dkv=8, ddim=64, dvdim=128, window=2048, keep=4, ff=14336, side=64,
+                  order="lds", vocab=32000),
+}
+
+
+def write_kiduvik(folder, z, context):
+    """A checkpoint directory of the given size: matrices tiled from one random block, norm weights 1, sinks and lambda vectors small."""
+    os.makedirs(folder, exist_ok=True)
+    rng = np.random.default_rng(4)
+    block = _bf16(rng.standard_normal(1 << 22).astype(np.float32) * 0.02)
+    W, n_layers = z["width"], len(z["order"])
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    lat = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"], "rot": {"base": 10000.0, "dims": z["rot"]},
+           "scale": (z["dim"] + z["rot"]) ** -0.5}
+    dif = {"heads": z["dheads"], "kv_heads": z["dkv"], "dim": z["ddim"], "vdim": z["dvdim"], "diff": 0.6, "mask": {"size": z["window"], "keep_first": z["keep"]},
+           "rot": {"base": 250000.0, "dims": z["ddim"] // 2, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}, "scale": z["ddim"] ** -0.5}
+    layers = [{"type": "latent_attention", "mixer": lat, "mlp": mlp} if c == "l" else
+              {"type": "latent_attention", "mixer": dict(lat, kv_from=z["order"].index("l")), "mlp": mlp} if c == "s" else
+              {"type": "attention", "mixer": dif, "mlp": mlp} for c in z["order"]]
+    cfg = {"architecture": "Kiduvik", "width": W, "vocab": z["vocab"], "max_positions": context, "norm": {"eps": 1e-5}, "token_side": {"dim": z["side"]},
+           "layers": layers}
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    shapes = {"embed": (z["vocab"], W), "pos": (context, W), "side.embed": (z["vocab"], n_layers * z["side"]), "final.norm": (W,), "head": (z["vocab"], W)}
+    for i, c in enumerate(z["order"]):
+        p, m, f, sd = "l%d." % i, "l%d.mix." % i, "l%d.mlp." % i, "l%d.side." % i
+        shapes.update({p + "norm1": (W,), p + "norm1b": (W,), p + "norm2": (W,), p + "norm2b": (W,), f + "up": (z["ff"], W), f + "down": (W, z["ff"]),
+                       sd + "gate": (z["side"], W), sd + "proj": (W, z["side"]), sd + "norm": (W,)})
+        if c in "ls":
+            H, no = z["heads"], z["heads"] * z["vdim"]
+            shapes.update({m + "q": (H * (z["dim"] + z["rot"]), W), m + "uk": (H * z["dim"], z["kv_rank"]), m + "uv": (no, z["kv_rank"]), m + "sink": (H,),
+                           m + "o": (W, no)})
+            if c == "l":
+                shapes.update({m + "dkv": (z["kv_rank"] + z["rot"], W), m + "dkv.norm": (z["kv_rank"],)})
+        else:
+            H, G, D = z["dheads"], z["dkv"], z["ddim"]
+            shapes.update({m + "q": (H * 2 * D, W), m + "k": (G * 2 * D, W), m + "v": (G * z["dvdim"], W), m + "q.norm": (D,), m + "k.norm": (D,),
+                           m + "lq1": (D,), m + "lk1": (D,), m + "lq2": (D,), m + "lk2": (D,), m + "g": (H, W), m + "o": (W, H * z["dvdim"])})
+    header, off = {}, 0
+    for name, shp in shapes.items():
+        n = int(np.prod(shp))
+        header[name] = {"dtype": "BF16", "shape": list(shp), "data_offsets": [off, off + 2 * n]}
+        off += 2 * n
+    h = json.dumps(header).encode()
+    h += b" " * (-len(h) % 8)
+    one = _bf16(np.ones(1, np.float32))[0]
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h)
+        for k, (name, shp) in enumerate(shapes.items()):
+            n = int(np.prod(shp))
+            last = name.split(".")[-1]
+            if last.startswith("norm"):
+                f.write(np.full(n, one, np.uint16).tobytes())
+            elif len(shp) < 2:
+                f.write(block[:n].tobytes())
+            else:
+                f.write(np.resize(np.roll(block, 7919 * k), n).tobytes())
+    return cfg
+
+
+def kiduvik_numbers(z):
+    """-> (decode bytes per token at CONTEXT, prefill FLOP per token): every matrix once (bf16); per latent-attention layer one cached
+    row per position for all heads over the whole context, per differential layer the window of both maps' keys and the values plus
+    the kept first tokens; 2 FLOP per parameter plus the attention's own products (latent: heads x (kv_rank + rot) per key for the
+    scores and kv_rank for the sums, over the causal half of the context on average in a prompt)."""
+    W = z["width"]
+    ffn = 2 * z["ff"] * W + 2 * z["side"] * W
+    params, cache, extra = z["vocab"] * W, 0, 0.0
+    for c in z["order"]:
+        if c in "ls":
+            H, no, row = z["heads"], z["heads"] * z["vdim"], z["kv_rank"] + z["rot"]
+            params += (H * (z["dim"] + z["rot"]) + (row if c == "l" else 0) + no) * W + H * (z["dim"] + z["vdim"]) * z["kv_rank"] + ffn
+            cache += CONTEXT * row * 2
+            extra += 2.0 * H * (CONTEXT / 2) * (z["dim"] + z["rot"] + z["vdim"])
+        else:
+            H, G, D, dv = z["dheads"], z["dkv"], z["ddim"], z["dvdim"]
+            seen = min(CONTEXT, z["window"])
+            params += (2 * H * D + 2 * G * D + G * dv + H + H * dv) * W + ffn
+            cache += seen * (2 * G * D + G * dv) * 2 + z["keep"] * (2 * G * D + G * dv) * 4
+            extra += 2.0 * 2 * H * (seen + z["keep"]) * (D + dv)
+    return 2 * params + cache, 2.0 * (params - z["vocab"] * W) + extra
+
+
+def run_kiduvik(args, base, emit, shm_path, ClockSampler):
+    """`bench.py --workload kiduvik-sizes`: the Kiduvik design beside the closest existing model on the same executor, the dense
+    Retezen stack (windowed attention with pooled blocks, a norm on every sublayer's output, learned positions, dense feed-forward),
+    at equal width, heads, head sizes, window, feed-forward size, layers and vocabulary."""
+    import torch
+    from yalm_b200 import api
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = json.load(open(pk)) if os.path.exists(pk) else {"hbm_gbs": 6650.0, "bf16_tflops_sustained": 1400.0}
+    hbm, tflops = float(peaks["hbm_gbs"]), float(peaks["bf16_tflops_sustained"])
+    steps = max(8, min(args.steps, 128))
+    clocks = ClockSampler(0)
+    clocks.start()
+    out, launches = [], 0
+
+    def measure(model, ids):
+        st = api.InferenceState(model)
+        st.forward_batch(ids[:1024], 0)                     # warm-up (sizes kernels, first-use set-up)
+        st.end_sequence()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        st.forward_batch(ids[:-1], 0)
+        t_pre = time.perf_counter() - t0
+        st.generate_greedy(ids[-1], CONTEXT - 1, max(3, args.warmup))   # first step eager + graph capture, untimed
+        st.generate_greedy(ids[0], CONTEXT - 1 + max(3, args.warmup), steps)
+        t_dec = st.device_ms / 1e3
+        n = model.launches()
+        st.close()
+        return (CONTEXT - 1) / t_pre, steps / t_dec, n
+
+    only = os.environ.get("YALM_BENCH_SIZES", "").split(",") if os.environ.get("YALM_BENCH_SIZES") else None
+    for name, z in KIDUVIK_SIZES.items():
+        if only and name not in only:
+            continue
+        ids = [(i * 7919 + 1) % z["vocab"] for i in range(CONTEXT)]
+        row = {"size": name, "width": z["width"], "layers": z["order"], "context": CONTEXT, "window": z["window"]}
+        folder = shm_path("yalm_bench_kiduvik_%s_%d" % (name, os.getpid()))
+        try:
+            write_kiduvik(folder, z, CONTEXT + steps + args.warmup + 8)
+            model = api.Model(folder, 0, api.BF16).cuda(0)
+        finally:
+            shutil.rmtree(folder, ignore_errors=True)
+        pre, dec, n = measure(model, ids)
+        model.close()
+        dec_bytes, pre_flop = kiduvik_numbers(z)
+        launches += steps * n
+        row["kiduvik"] = {"prefill_tok_s": pre, "decode_tok_s": dec, "prefill_frac_of_measured_bf16": pre_flop * pre / 1e12 / tflops,
+                          "decode_frac_of_measured_hbm": dec_bytes * dec / 1e9 / hbm, "decode_bytes_per_token": dec_bytes, "launches_per_token": n}
+        if not os.environ.get("YALM_BENCH_NO_PEER"):
+            zr = dict(SIZES[name], layers=len(z["order"]))
+            folder = shm_path("yalm_bench_retezen_peer_%s_%d" % (name, os.getpid()))
+            try:
+                write_retezen(folder, zr, "dense", CONTEXT + steps + args.warmup + 8)
+                model = api.Model(folder, 0, api.BF16).cuda(0)
+            finally:
+                shutil.rmtree(folder, ignore_errors=True)
+            pre, dec, n = measure(model, ids)
+            model.close()
+            _, r_bytes, r_flop = retezen_numbers(zr, "dense")
+            row["equal_size_retezen"] = {"prefill_tok_s": pre, "decode_tok_s": dec, "prefill_frac_of_measured_bf16": r_flop * pre / 1e12 / tflops,
+                                         "decode_frac_of_measured_hbm": r_bytes * dec / 1e9 / hbm, "decode_bytes_per_token": r_bytes, "launches_per_token": n}
+        out.append(row)
+    clk = clocks.stop()
+    first = out[0]["kiduvik"]
+    emit(dict(base, impl="ours", metric="batch-1 decode tok/s (Kiduvik, first size; all sizes under `sizes`)", value=first["decode_tok_s"], steps=steps,
+              ms_per_step=1000.0 / first["decode_tok_s"], dtype="bf16", clocks=clk, gpu_launches=launches, sizes=out,
+              e2e={"value": first["decode_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 4,
+                   "note": "device loop: token ids stay on the device, 4 bytes per token come back"},
+              config=dict(base["config"], workload="Kiduvik at model-like sizes beside the equal-size dense Retezen stack", context=CONTEXT,
+                          l2="inputs larger than L2 (weights streamed per token)")))
+
+
 def run(args, base, emit, write_yalm, shm_path, ClockSampler):
     import torch
     from yalm_b200 import api
