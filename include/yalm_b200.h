@@ -416,6 +416,15 @@ int yalm_act_rows(float *h, int ld, int n, int ff, int act, yalm_stream_t s);
 int yalm_token_side_rows(float *x, const void *table, int ldt, int col0, const int *tokens, const int *ctl, const void *w_gate, const void *w_proj,
                          const float *norm_w, int dtype, int n, int dim, int side, float eps, yalm_stream_t s);
 
+/* The side input in two steps that spread over the GPU: h[m, j] = gelu_tanh(w_gate[j] . x[m]) * table[token of row m, col0 + j]; with
+ * w_gate NULL, h already holds the product x w_gate^T and is finished in place.  dim % 8 == 0 (fp32: 4), 16-byte aligned rows. */
+int yalm_token_side_gate_rows(float *h, int ldh, const float *x, int ldx, const void *table, int ldt, int col0, const int *tokens, const int *ctl,
+                              const void *w_gate, int dtype, int n, int dim, int side, yalm_stream_t s);
+/* yalm_gemv_norm_residual (no weight offset) with a plain activation on the input (act >= 0: yalm_act_rows' codes, applied while x is
+ * staged; negative: none) and, if next_w, the next sublayer's input norm from the finished row: next_out = rms(res) * next_w. */
+int yalm_gemv_act_norm_residual_norm(float *res, float *y, const float *x, const void *w, const float *nw, float eps, int n, int d, int dtype, int act,
+                                     const float *next_w, float *next_out, unsigned *counter, yalm_stream_t s);
+
 /* ---- (3a) host-pointer test entry points (src/infer.cu:890-1007 semantics) ------------------- */
 int yalm_matmul_host(float *xout, const float *x, const void *w, const float *scale, int n, int d, int dtype);
 int yalm_mha_host(float *xout, float *att, const uint16_t *kb, const uint16_t *vb, const float *q, int head_dim,

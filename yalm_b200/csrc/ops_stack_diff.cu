@@ -95,12 +95,6 @@ __global__ void __launch_bounds__(256) diff_combine_rows_kernel(float *__restric
 }
 
 // ---- a plain activation, in place ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float act_value(float z, int act) {
-	if (act == 4) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));                                   // exact GELU
-	if (act == 3) return 0.5f * z * (1.0f + tanhf(0.7978845608f * (z + 0.044715f * z * z * z)));              // tanh GELU
-	if (act == YALM_ACT_SILU) return act_silu(z);
-	return act_gelu(z);
-}
 __global__ void act_rows_kernel(float *__restrict__ h, int ld, int ff, int act) {
 	float *row = h + (size_t)blockIdx.y * ld;
 	for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < ff; f += gridDim.x * blockDim.x) row[f] = act_value(row[f], act);
@@ -136,6 +130,30 @@ __global__ void __launch_bounds__(256) token_side_rows_kernel(float *__restrict_
 	ss = block_sum(ss, red);
 	const float r = 1.0f / sqrtf(ss / (float)dim + eps);
 	for (int e = threadIdx.x; e < dim; e += blockDim.x) row[e] += ys[e] * r * nw[e];
+}
+
+
+// The same in two steps that spread over the GPU, for sizes that are 16-byte multiples: h = gelu_tanh(G x) * e (a warp per gate
+// row and row of x; or, after a tensor-core product g = x G^T, in place), then the products' usual routes for y = P h and the norm.
+template <int DT>
+__global__ void __launch_bounds__(128) token_side_gate_rows_kernel(float *__restrict__ h, int ldh, const float *__restrict__ x, int ldx,
+                                                                   const void *__restrict__ table, int ldt, int col0, const int *__restrict__ tokens,
+                                                                   const int *__restrict__ ctl, const void *__restrict__ wg, int dim, int sd) {
+	const int m = blockIdx.y, j = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+	if (j >= sd) return;
+	const float z = warp_dot<DT>(wg, (size_t)j * dim, x + (size_t)m * ldx, dim, true);
+	if ((threadIdx.x & 31) == 0) {
+		const int token = tokens ? tokens[m] : ctl[CTL_TOKEN];
+		h[(size_t)m * ldh + j] = act_value(z, 3) * Elem<DT>::get(table, (size_t)token * ldt + col0 + j);
+	}
+}
+template <int DT>
+__global__ void token_side_act_rows_kernel(float *__restrict__ h, int ldh, const void *__restrict__ table, int ldt, int col0, const int *__restrict__ tokens,
+                                           const int *__restrict__ ctl, int sd) {
+	const int m = blockIdx.y;
+	const int token = tokens ? tokens[m] : ctl[CTL_TOKEN];
+	for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < sd; j += gridDim.x * blockDim.x)
+		h[(size_t)m * ldh + j] = act_value(h[(size_t)m * ldh + j], 3) * Elem<DT>::get(table, (size_t)token * ldt + col0 + j);
 }
 
 } // namespace stack
@@ -193,5 +211,29 @@ extern "C" int yalm_token_side_rows(float *x, const void *table, int ldt, int co
 	else if (dtype == YALM_BF16) SIDE_CASE(YALM_BF16)
 	else return YALM_EINVAL;
 #undef SIDE_CASE
+	return (int)cudaGetLastError();
+}
+
+// h[m, j] = gelu_tanh(w_gate[j] . x[m]) * table[token of row m, col0 + j] (g NULL), or the same from a product g = x w_gate^T that
+// h already holds (w_gate NULL).  dim % 8 == 0 (fp32: 4), 16-byte aligned rows.
+extern "C" int yalm_token_side_gate_rows(float *h, int ldh, const float *x, int ldx, const void *table, int ldt, int col0, const int *tokens, const int *ctl,
+                                         const void *w_gate, int dtype, int n, int dim, int side, yalm_stream_t s) {
+	if (!h || !table || (!tokens && !ctl) || n < 1 || side < 1 || col0 < 0 || col0 + side > ldt) return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	if (!w_gate) {
+		const dim3 grid(std::min(8, (side + 127) / 128), n);
+		if (dtype == YALM_F32) token_side_act_rows_kernel<YALM_F32><<<grid, 128, 0, st>>>(h, ldh, table, ldt, col0, tokens, ctl, side);
+		else if (dtype == YALM_F16) token_side_act_rows_kernel<YALM_F16><<<grid, 128, 0, st>>>(h, ldh, table, ldt, col0, tokens, ctl, side);
+		else if (dtype == YALM_BF16) token_side_act_rows_kernel<YALM_BF16><<<grid, 128, 0, st>>>(h, ldh, table, ldt, col0, tokens, ctl, side);
+		else return YALM_EINVAL;
+		return (int)cudaGetLastError();
+	}
+	const int vec = dtype == YALM_F32 ? 4 : 8;
+	if (!x || dim < 1 || dim % vec || ldx % 4 || ((uintptr_t)x & 15) || ((uintptr_t)w_gate & 15)) return YALM_EINVAL;
+	const dim3 grid((side + 3) / 4, n);
+	if (dtype == YALM_F32) token_side_gate_rows_kernel<YALM_F32><<<grid, 128, 0, st>>>(h, ldh, x, ldx, table, ldt, col0, tokens, ctl, w_gate, dim, side);
+	else if (dtype == YALM_F16) token_side_gate_rows_kernel<YALM_F16><<<grid, 128, 0, st>>>(h, ldh, x, ldx, table, ldt, col0, tokens, ctl, w_gate, dim, side);
+	else if (dtype == YALM_BF16) token_side_gate_rows_kernel<YALM_BF16><<<grid, 128, 0, st>>>(h, ldh, x, ldx, table, ldt, col0, tokens, ctl, w_gate, dim, side);
+	else return YALM_EINVAL;
 	return (int)cudaGetLastError();
 }

@@ -31,7 +31,7 @@ struct GemvTailArgs {
 	const char *w;
 	int n, d;
 	float alpha;
-	// head: glu != 0: x[f] = glu_value(x[f], x[n + f]) of a (gate | up) row of 2 n floats
+	// head: glu == 1: x[f] = glu_value(x[f], x[n + f]) of a (gate | up) row of 2 n floats; glu == 2: x[f] = act_value(x[f]), no gate
 	int glu, act;
 	float act_alpha, limit, up_offset;
 	// tail
@@ -39,6 +39,8 @@ struct GemvTailArgs {
 	unsigned *counter;
 	float *res;          // 1: the residual row (d)
 	const float *nw;     // 1: norm weight
+	const float *next_w; // 1, optional: the next sublayer's input norm, next_out = rms(res) next_w, from the finished residual row
+	float *next_out;
 	float woff, eps;
 	void *kring, *vring; // 2
 	float *vfirst, *kpool, *vpool;
@@ -69,7 +71,13 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_tail_kernel(GemvTailArgs a)
 	const int warps = (gridDim.x * blockDim.x) >> 5, gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
 	const size_t row_bytes = (size_t)a.n * B;
 	const int ntasks = (a.d + R - 1) / R;
-	if (a.glu) {
+	if (a.glu == 2) {
+		for (int e = threadIdx.x * 4; e < a.n; e += blockDim.x * 4) {
+			float4 v = *reinterpret_cast<const float4 *>(a.x + e);
+			v.x = act_value(v.x, a.act), v.y = act_value(v.y, a.act), v.z = act_value(v.z, a.act), v.w = act_value(v.w, a.act);
+			*reinterpret_cast<float4 *>(xs + xs_slot<EP>(e)) = v;
+		}
+	} else if (a.glu) {
 		for (int e = threadIdx.x * 4; e < a.n; e += blockDim.x * 4) {
 			const float4 g = *reinterpret_cast<const float4 *>(a.x + e), u = *reinterpret_cast<const float4 *>(a.x + a.n + e);
 			float4 v;
@@ -121,6 +129,13 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_tail_kernel(GemvTailArgs a)
 	__threadfence();
 	if (a.tail == 1) {
 		norm_residual_row(a.res, a.out, 0, 1, a.nw, a.woff, a.eps, a.d, xs, red); // xs: free now, sized for max(n, d) by the launcher
+		if (a.next_w) { // every thread reads back the elements it has just written
+			float ss = 0.f;
+			for (int e = threadIdx.x; e < a.d; e += blockDim.x) ss += a.res[e] * a.res[e];
+			ss = block_sum(ss, red);
+			const float r = 1.0f / sqrtf(ss / a.d + a.eps);
+			for (int e = threadIdx.x; e < a.d; e += blockDim.x) a.next_out[e] = a.res[e] * r * a.next_w[e];
+		}
 	} else if (a.tail == 3) { // every CTA has staged its input from the old state
 		for (int e = threadIdx.x; e < a.n; e += blockDim.x) a.hstate[e] = __ldcg(a.hout + e);
 	} else if (a.tail == 4) {
@@ -252,5 +267,24 @@ extern "C" int yalm_gemv_residual_sum(float *res, float *y, const float *x, cons
 	GemvTailArgs a{};
 	a.out = y, a.x = x, a.w = (const char *)w, a.n = n, a.d = d, a.alpha = alpha;
 	a.tail = 4, a.counter = counter, a.res = res, a.add1 = add1, a.slots = slots, a.nslots = nslots, a.ldslots = ldslots;
+	return launch_tail(a, dtype, (cudaStream_t)s);
+}
+
+// yalm_gemv_norm_residual with a plain activation on the input (act >= 0: x[f] = act(x[f]) while it is staged; yalm_act_rows'
+// codes) and, optionally, the next sublayer's input norm from the finished residual row: next_out = rms(res) * next_w.
+extern "C" int yalm_gemv_act_norm_residual_norm(float *res, float *y, const float *x, const void *w, const float *nw, float eps, int n, int d, int dtype, int act,
+                                                const float *next_w, float *next_out, unsigned *counter, yalm_stream_t s) {
+	if (!res || !nw || (next_w && !next_out)) return YALM_EINVAL;
+	GemvTailArgs a{};
+	a.out = y, a.x = x, a.w = (const char *)w, a.n = n, a.d = d, a.alpha = 1.f;
+	a.glu = act >= 0 ? 2 : 0, a.act = act;
+	a.tail = 1, a.counter = counter, a.res = res, a.nw = nw, a.woff = 0.f, a.eps = eps, a.next_w = next_w, a.next_out = next_out;
+	if (tail_separate()) {
+		a.tail = 0;
+		int rc = launch_tail(a, dtype, (cudaStream_t)s);
+		if (!rc) rc = yalm_norm_residual_rows(res, y, d, 1, nw, 0.f, eps, 1, d, s);
+		if (!rc && next_w) rc = yalm_norm_shift_rows(next_out, nullptr, res, next_w, 0, 0.f, eps, nullptr, nullptr, 1, d, 0, nullptr, s);
+		return rc;
+	}
 	return launch_tail(a, dtype, (cudaStream_t)s);
 }

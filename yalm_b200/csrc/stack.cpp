@@ -261,6 +261,7 @@ struct Model::StackScratch {
 	int *order = nullptr;                       // slot at every place of that order
 	unsigned *ticket = nullptr; // arrival counter of the one-row products with a fused tail (zero between launches)
 	int hist_slabs = 0;
+	bool xn_valid = false;    // xn already holds the next sublayer's normed input (left there by the previous product's tail)
 	std::vector<Placement> placements; // filled by build_stack, consumed by cuda_stack
 	// decode rows of a parallel block: its independent sublayers (experts, the second mixer) run on side streams that fork from and
 	// join the caller's stream through these events; inside a captured step they become parallel branches of the graph
@@ -1103,7 +1104,13 @@ static int plain_act_code(yalm::GluAct a) {
 // part] (its own, or another layer's), or differential attention: (map, head) is one list of attention heads over rings that
 // hold (map, kv head) key vectors and kv heads values, the window's kept first tokens are read like pooled blocks of one token,
 // and the two maps of a head are combined afterwards.  What the rows leave for the next call is written by the ops themselves.
-int Model::stack_layer_sandwich(StackScratch &S, const yalm::StackLayer &L, int index, int n, int pos0, const int *ctl, bool from_ctl, cudaStream_t st) {
+static bool side_one_kernel() { // YALM_STACK_SIDE=0: the token side input as one launch of one CTA per row (the route of sizes that are no 16-byte multiples)
+	static const bool on = [] { const char *e = getenv("YALM_STACK_SIDE"); return e && e[0] == '0'; }();
+	return on;
+}
+
+int Model::stack_layer_sandwich(StackScratch &S, const yalm::StackLayer &L, const yalm::StackLayer *next, int index, int n, int pos0, const int *ctl,
+                                bool from_ctl, cudaStream_t st) {
 	const Config &c = *config;
 	const StackSpec &sp = *c.stack;
 	const yalm::LayerSpec &ls = L.spec;
@@ -1111,8 +1118,16 @@ int Model::stack_layer_sandwich(StackScratch &S, const yalm::StackLayer &L, int 
 	const int dt = static_cast<int>(c.weight_dtype), W = sp.width, f32 = c.weight_dtype == DType::F32;
 	const int ldp = ls.proj_width(), no = m.heads * m.vdim;
 	float *P = S.qkv;
+	const FfnSpec &f = ls.ffn;
+	const bool side = sp.token_side > 0;
+	// A decode row's products end in a tail that has the finished residual row in one CTA: the next sublayer's input norm rides along
+	// (xn_valid tells the next sublayer), so that only the first layer of a step launches a norm of its own.
+	const float *norm_after_mixer = f.kind == FfnSpec::Dense ? L.norm2 : (side || !next) ? nullptr : next->norm1;
+	const float *norm_after_ffn = (side || !next) ? nullptr : next->norm1;
+	const float *norm_after_side = next ? next->norm1 : nullptr;
 	// ---- token mixer ----
-	ST_TRY(yalm_norm_shift_rows(S.xn, nullptr, S.x, L.norm1, 0, 0.f, sp.norm_eps, nullptr, nullptr, n, W, pos0, ctl, st));
+	if (!S.xn_valid) ST_TRY(yalm_norm_shift_rows(S.xn, nullptr, S.x, L.norm1, 0, 0.f, sp.norm_eps, nullptr, nullptr, n, W, pos0, ctl, st));
+	S.xn_valid = false;
 	if (ls.kind == yalm::MixerKind::LatentAttention) {
 		const yalm::LatentSpec &a = ls.latent;
 		const int row = a.kv_rank + a.rot_dim, nqa = m.heads * row, nl = m.heads * a.kv_rank, dk = m.dim + a.rot_dim;
@@ -1163,37 +1178,61 @@ int Model::stack_layer_sandwich(StackScratch &S, const yalm::StackLayer &L, int 
 		ST_TRY(yalm_diff_combine_rows(S.att, no, S.scan, na, m.head_gate ? P + L.o_gate : nullptr, ldp, n, m.heads, m.vdim, L.lambda, 1.f - m.diff, sp.norm_eps, st));
 	}
 	// output projection, the norm on its result and the residual add: one launch for a decode row
-	if (gemv_fusable(c, n, no, L.wo, S.att))
-		ST_TRY(yalm_gemv_norm_residual(S.x, S.y1, S.att, L.wo, L.norm1b, 0.f, sp.norm_eps, no, W, dt, 0, 0, 0.f, 0.f, 0.f, S.ticket, st));
-	else {
+	if (gemv_fusable(c, n, no, L.wo, S.att)) {
+		ST_TRY(yalm_gemv_act_norm_residual_norm(S.x, S.y1, S.att, L.wo, L.norm1b, sp.norm_eps, no, W, dt, -1, norm_after_mixer, S.xn, S.ticket, st));
+		S.xn_valid = norm_after_mixer != nullptr;
+	} else {
 		ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.att, no, L.wo, n, W, no, 1.f, st));
 		ST_TRY(yalm_norm_residual_rows(S.x, S.y1, W, 1, L.norm1b, 0.f, sp.norm_eps, n, W, st));
 	}
 	// ---- feed-forward ----
-	const FfnSpec &f = ls.ffn;
 	if (f.kind == FfnSpec::Dense) {
-		ST_TRY(yalm_norm_shift_rows(S.xn, nullptr, S.x, L.norm2, 0, 0.f, sp.norm_eps, nullptr, nullptr, n, W, pos0, ctl, st));
-		const float *hid;
+		if (!S.xn_valid) ST_TRY(yalm_norm_shift_rows(S.xn, nullptr, S.x, L.norm2, 0, 0.f, sp.norm_eps, nullptr, nullptr, n, W, pos0, ctl, st));
+		S.xn_valid = false;
 		if (f.gated) {
 			ST_TRY(stack_linear(*this, c, S.a16, S.gu, 2 * f.ff, S.xn, W, L.wgu, n, 2 * f.ff, W, 1.f, st));
-			ST_TRY(yalm_glu_act_rows(S.h, S.gu, n, f.ff, glu_act_code(f.act), f.act_alpha, f.limit, f.up_offset, st));
-			hid = S.h;
+			if (gemv_fusable(c, n, f.ff, L.wdown, S.gu) && (size_t)f.ff * 4 % 16 == 0)
+				ST_TRY(yalm_gemv_norm_residual(S.x, S.y1, S.gu, L.wdown, L.norm2b, 0.f, sp.norm_eps, f.ff, W, dt, 1, glu_act_code(f.act), f.act_alpha, f.limit,
+				                               f.up_offset, S.ticket, st));
+			else {
+				ST_TRY(yalm_glu_act_rows(S.h, S.gu, n, f.ff, glu_act_code(f.act), f.act_alpha, f.limit, f.up_offset, st));
+				ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.h, f.ff, L.wdown, n, W, f.ff, 1.f, st));
+				ST_TRY(yalm_norm_residual_rows(S.x, S.y1, W, 1, L.norm2b, 0.f, sp.norm_eps, n, W, st));
+			}
 		} else {
 			ST_TRY(stack_linear(*this, c, S.a16, S.gu, f.ff, S.xn, W, L.wgu, n, f.ff, W, 1.f, st));
-			ST_TRY(yalm_act_rows(S.gu, f.ff, n, f.ff, plain_act_code(f.act), st));
-			hid = S.gu;
-		}
-		if (gemv_fusable(c, n, f.ff, L.wdown, hid))
-			ST_TRY(yalm_gemv_norm_residual(S.x, S.y1, hid, L.wdown, L.norm2b, 0.f, sp.norm_eps, f.ff, W, dt, 0, 0, 0.f, 0.f, 0.f, S.ticket, st));
-		else {
-			ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, hid, f.ff, L.wdown, n, W, f.ff, 1.f, st));
-			ST_TRY(yalm_norm_residual_rows(S.x, S.y1, W, 1, L.norm2b, 0.f, sp.norm_eps, n, W, st));
+			if (gemv_fusable(c, n, f.ff, L.wdown, S.gu)) { // the activation is applied while the down projection stages its input
+				ST_TRY(yalm_gemv_act_norm_residual_norm(S.x, S.y1, S.gu, L.wdown, L.norm2b, sp.norm_eps, f.ff, W, dt, plain_act_code(f.act), norm_after_ffn, S.xn,
+				                                        S.ticket, st));
+				S.xn_valid = norm_after_ffn != nullptr;
+			} else {
+				ST_TRY(yalm_act_rows(S.gu, f.ff, n, f.ff, plain_act_code(f.act), st));
+				ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.gu, f.ff, L.wdown, n, W, f.ff, 1.f, st));
+				ST_TRY(yalm_norm_residual_rows(S.x, S.y1, W, 1, L.norm2b, 0.f, sp.norm_eps, n, W, st));
+			}
 		}
 	}
 	// ---- token side input ----
-	if (sp.token_side > 0)
-		ST_TRY(yalm_token_side_rows(S.x, _side_table, sp.token_side * (int)sp.layers.size(), index * sp.token_side, from_ctl ? nullptr : S.tokens, ctl, L.side_gate,
-		                            L.side_proj, L.side_norm, dt, n, W, sp.token_side, sp.norm_eps, st));
+	if (side) {
+		const int sd = sp.token_side, ldt = sd * (int)sp.layers.size(), col0 = index * sd;
+		const int *toks = from_ctl ? nullptr : S.tokens;
+		if (sd % 8 == 0 && W % 8 == 0 && !side_one_kernel()) {
+			// h = gelu_tanh(G x) * e: many rows through the tensor-core product, few as one warp per gate row; then y = P h like any product
+			if (!f32 && n >= 32) {
+				ST_TRY(stack_linear(*this, c, S.a16, S.gu, sd, S.x, W, L.side_gate, n, sd, W, 1.f, st));
+				ST_TRY(yalm_token_side_gate_rows(S.gu, sd, nullptr, 0, _side_table, ldt, col0, toks, ctl, nullptr, dt, n, W, sd, st));
+			} else
+				ST_TRY(yalm_token_side_gate_rows(S.gu, sd, S.x, W, _side_table, ldt, col0, toks, ctl, L.side_gate, dt, n, W, sd, st));
+			if (gemv_fusable(c, n, sd, L.side_proj, S.gu)) {
+				ST_TRY(yalm_gemv_act_norm_residual_norm(S.x, S.y1, S.gu, L.side_proj, L.side_norm, sp.norm_eps, sd, W, dt, -1, norm_after_side, S.xn, S.ticket, st));
+				S.xn_valid = norm_after_side != nullptr;
+			} else {
+				ST_TRY(stack_linear(*this, c, S.a16, S.y1, W, S.gu, sd, L.side_proj, n, W, sd, 1.f, st));
+				ST_TRY(yalm_norm_residual_rows(S.x, S.y1, W, 1, L.side_norm, 0.f, sp.norm_eps, n, W, st));
+			}
+		} else
+			ST_TRY(yalm_token_side_rows(S.x, _side_table, ldt, col0, toks, ctl, L.side_gate, L.side_proj, L.side_norm, dt, n, W, sd, sp.norm_eps, st));
+	}
 	return 0;
 }
 
@@ -1217,7 +1256,9 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 		++layer_no;
 		return 0;
 	};
-	for (auto &Lp : _stack) {
+	S.xn_valid = false;
+	for (size_t li = 0; li < _stack.size(); ++li) {
+		auto &Lp = _stack[li];
 		const StackLayer &L = *Lp;
 		if (sp.parallel_block) {
 			ST_TRY(stack_layer_parallel(S, L, n, pos0, ctl, st));
@@ -1225,7 +1266,7 @@ int Model::stack_pass(InferenceState &s, int n, int pos0, bool from_ctl, int n_w
 			continue;
 		}
 		if (L.sandwich) {
-			ST_TRY(stack_layer_sandwich(S, L, layer_no, n, pos0, ctl, from_ctl, st));
+			ST_TRY(stack_layer_sandwich(S, L, li + 1 < _stack.size() ? _stack[li + 1].get() : nullptr, layer_no, n, pos0, ctl, from_ctl, st));
 			ST_TRY(tap());
 			continue;
 		}

@@ -115,6 +115,14 @@ __device__ __forceinline__ float glu_value(float g, float u, int act, float alph
 	return a * (u + up_offset);
 }
 
+// a plain activation: 4 the exact GELU, 3 the tanh GELU, else SiLU / the .yalm models' GELU
+__device__ __forceinline__ float act_value(float z, int act) {
+	if (act == 4) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));                                   // exact GELU
+	if (act == 3) return 0.5f * z * (1.0f + tanhf(0.7978845608f * (z + 0.044715f * z * z * z)));              // tanh GELU
+	if (act == YALM_ACT_SILU) return act_silu(z);
+	return act_gelu(z);
+}
+
 // Row `row` of q | k | v (fp32) at ring slot `slot`: RMS norm over the WHOLE q and k projections (all heads at once), one
 // weight per channel (qnorm / knorm null: left as they are); q stays in place, k goes to the ring.  v: vmode 1 keeps a copy
 // in vfirst (the first blending layer), vmode 2 blends v = (1 - lambda) v + lambda vfirst (later blending layers); the

@@ -340,7 +340,8 @@ private:
 	int stack_moe_grouped(StackScratch &S, const yalm::StackLayer &L, const float *x, void *a16, int n, int act, cudaStream_t st);
 	int stack_layer_parallel(StackScratch &S, const yalm::StackLayer &L, int n, int pos0, const int *ctl, cudaStream_t st);
 	int stack_layer_prenorm(StackScratch &S, const yalm::StackLayer &L, int index, int n, int pos0, const int *ctl, cudaStream_t st);
-	int stack_layer_sandwich(StackScratch &S, const yalm::StackLayer &L, int index, int n, int pos0, const int *ctl, bool from_ctl, cudaStream_t st);
+	int stack_layer_sandwich(StackScratch &S, const yalm::StackLayer &L, const yalm::StackLayer *next, int index, int n, int pos0, const int *ctl, bool from_ctl,
+	                         cudaStream_t st);
 	int stack_generate(InferenceState &s, int token, int pos, int n_gen, float temperature, unsigned long long seed, int *tokens_out,
 	                   float *logits_out, float *device_ms);
 	Device _device = Device::CPU;
