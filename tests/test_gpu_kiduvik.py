@@ -281,6 +281,36 @@ def test_token_side_input(W, sd, dt, tt):
     close_enough(xd.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("dt,tt", [(api.F32, torch.float32), (api.BF16, torch.bfloat16)])
+@pytest.mark.parametrize("n", [1, 5, 40])
+def test_token_side_input_in_steps(n, dt, tt):
+    """The spread route: gate rows per warp (or finished in place after a product), then the projection with the norm as its tail."""
+    rng = np.random.default_rng(n)
+    W, sd, V, layers, layer, eps = 96, 16, 30, 2, 1, 1e-5
+    w = {"side.embed": O.bf16_round(rng.standard_normal((V, layers * sd))), "l1.side.gate": O.bf16_round(rng.standard_normal((sd, W)) / math.sqrt(W)),
+         "l1.side.proj": O.bf16_round(rng.standard_normal((W, sd))), "l1.side.norm": 0.5 + rng.standard_normal(W)}
+    x, toks = rng.standard_normal((n, W)), rng.integers(0, V, n)
+    e = w["side.embed"][toks][:, layer * sd:(layer + 1) * sd]
+    want_h = O.gelu_tanh(x @ w["l1.side.gate"].T) * e
+    xd, tab, tk, wg = dev(x), dev(w["side.embed"], tt), dev(toks, torch.int32), dev(w["l1.side.gate"], tt)
+    h = torch.zeros((n, sd + 4), device="cuda")
+    ok(L().yalm_token_side_gate_rows(ptr(h), sd + 4, ptr(xd), W, ptr(tab), layers * sd, layer * sd, ptr(tk), None, ptr(wg), dt, n, W, sd, None), "token_side_gate_rows")
+    close_enough(h.cpu().numpy()[:, :sd], want_h)
+    g = dev(x @ w["l1.side.gate"].T)
+    ok(L().yalm_token_side_gate_rows(ptr(g), sd, None, 0, ptr(tab), layers * sd, layer * sd, ptr(tk), None, None, dt, n, W, sd, None), "token_side_gate_rows in place")
+    close_enough(g.cpu().numpy(), want_h)
+    # the projection of one row with the norm + residual tail, the next sublayer's norm riding along, and an activation on the input
+    nw, nxt, wp = 0.5 + rng.standard_normal(W), 1 + 0.2 * rng.standard_normal(W), dev(w["l1.side.proj"], tt)
+    for act, fn in ((-1, lambda z: z), (4, O.gelu_erf), (3, O.gelu_tanh)):
+        res, y, out, cnt = dev(x[0]), torch.zeros(W, device="cuda"), torch.zeros(W, device="cuda"), torch.zeros(64, dtype=torch.int32, device="cuda")
+        nwd, nxd, hd = dev(nw), dev(nxt), dev(want_h[0])
+        ok(L().yalm_gemv_act_norm_residual_norm(ptr(res), ptr(y), ptr(hd), ptr(wp), ptr(nwd), f32(eps), sd, W, dt, act, ptr(nxd), ptr(out), ptr(cnt), None), "gemv_act_norm_residual_norm")
+        want_x = x[0] + O.rms_norm(fn(want_h[0]) @ w["l1.side.proj"].T, nw, eps)
+        close_enough(res.cpu().numpy(), want_x)
+        close_enough(out.cpu().numpy(), O.rms_norm(want_x, nxt, eps))
+        assert int(cnt[0]) == 0
+
+
 # ---- small models -----------------------------------------------------------------------------------------------------------------
 def open_model(folder, dtype=api.F32, chunk=None, context=0):
     old = os.environ.get("YALM_STACK_CHUNK")
@@ -380,6 +410,28 @@ def test_every_layer_of_a_mixed_model(tmp_path):
     for i in range(5):
         close_enough(buf[i], after[i])
     close_enough(got, want)
+
+
+@pytest.mark.parametrize("dtype,tol", [(api.F32, F32_TOL), (api.BF16, 5e-2)])
+def test_sizes_that_are_no_vector_multiple(tmp_path, dtype, tol):
+    """Nothing here is a multiple of 8 (some not of 4): every op takes its scalar route, rows of caches and weights start at odd offsets."""
+    cfg = O.make_config([
+        O.latent_mixer(heads=3, dim=10, rot_dim=6, vdim=14, kv_rank=18),
+        O.diff_mixer(heads=3, kv_heads=1, dim=10, vdim=6, size=9, keep_first=2, rot_dims=4),
+        O.latent_mixer(heads=2, dim=5, rot_dim=6, vdim=7, kv_rank=18, kv_from=0),
+        O.diff_mixer(heads=5, kv_heads=5, dim=6, vdim=11, size=4, keep_first=1, rot_dims=6, scaling=False),
+    ], width=52, vocab=51, ff=36, side=5)
+    folder, W = checkpoint(tmp_path, cfg, seed=12)
+    T = 45
+    toks = tokens_for(cfg, T)
+    want, _ = O.forward(cfg, W, toks)
+    m, s = open_model(folder, dtype)
+    whole = s.forward_rows(toks, 0, range(T))
+    s.end_sequence()
+    parts = np.concatenate([s.forward_rows(toks[at:at + n], at, range(n)) for at, n in portions(T, [1, 2, 33, 1, 5])])
+    close(m, s)
+    close_enough(whole, want, tol)
+    close_enough(parts, want, tol)
 
 
 def test_a_left_out_sink_or_a_shifted_window_would_show(tmp_path):
