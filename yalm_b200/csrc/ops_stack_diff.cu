@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(kHnWarps * 32) head_norm_rope_append_rows_kern
 	const int m = blockIdx.x, p = first_pos(ctl, pos0) + m, slot = p % ring;
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, half = rot_dims / 2;
 	float *row = P + (size_t)m * ld, *vs = buf[warp];
-	for (int v = warp; v < nqv + nkv; v += kHnWarps) {
+	for (int v = blockIdx.y * kHnWarps + warp; v < nqv + nkv; v += gridDim.y * kHnWarps) { // grid.y spreads a row's vectors over CTAs
 		const bool is_q = v < nqv;
 		float *src = row + (is_q ? o_q + (size_t)v * dk : o_k + (size_t)(v - nqv) * dk);
 		const float *w = is_q ? qw : kw;
@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(kHnWarps * 32) head_norm_rope_append_rows_kern
 		}
 		__syncwarp();
 	}
-	for (int e = threadIdx.x; e < nvh * dv; e += blockDim.x) {
+	for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < nvh * dv; e += gridDim.y * blockDim.x) {
 		const int g = e / dv, d = e % dv;
 		CT *dst = vring + ((size_t)g * ring + slot) * dv;
 		cache_put(dst, d, row[o_v + e]);
@@ -170,12 +170,14 @@ extern "C" int yalm_head_norm_rope_append_rows(float *proj, int ld, int o_q, int
 	    (rot_dims > 0 && !freq) || keep < 0 || (keep > 0 && (!key_first || !value_first)))
 		return YALM_EINVAL;
 	cudaStream_t st = (cudaStream_t)s;
+	// every load of a vector's chain (channels, norm, rotation, store) waits for the one before it: enough warps in flight hide that
+	const dim3 grid(n, std::max(1, std::min((n_q_vectors + n_k_vectors + kHnWarps - 1) / kHnWarps, n >= 64 ? 4 : 16)));
 	if (cache_f32)
-		head_norm_rope_append_rows_kernel<float><<<n, kHnWarps * 32, 0, st>>>(proj, ld, o_q, o_k, o_v, n_q_vectors, n_k_vectors, n_v_heads, dk, dv, q_norm, k_norm,
+		head_norm_rope_append_rows_kernel<float><<<grid, kHnWarps * 32, 0, st>>>(proj, ld, o_q, o_k, o_v, n_q_vectors, n_k_vectors, n_v_heads, dk, dv, q_norm, k_norm,
 		                                                                       freq, magnitude, rot_dims, interleaved, eps, (float *)key_ring, (float *)value_ring,
 		                                                                       ring, key_first, value_first, keep, pos0, ctl);
 	else
-		head_norm_rope_append_rows_kernel<__nv_bfloat16><<<n, kHnWarps * 32, 0, st>>>(proj, ld, o_q, o_k, o_v, n_q_vectors, n_k_vectors, n_v_heads, dk, dv, q_norm,
+		head_norm_rope_append_rows_kernel<__nv_bfloat16><<<grid, kHnWarps * 32, 0, st>>>(proj, ld, o_q, o_k, o_v, n_q_vectors, n_k_vectors, n_v_heads, dk, dv, q_norm,
 		                                                                               k_norm, freq, magnitude, rot_dims, interleaved, eps,
 		                                                                               (__nv_bfloat16 *)key_ring, (__nv_bfloat16 *)value_ring, ring, key_first,
 		                                                                               value_first, keep, pos0, ctl);
