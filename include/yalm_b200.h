@@ -425,6 +425,15 @@ int yalm_token_side_gate_rows(float *h, int ldh, const float *x, int ldx, const 
 int yalm_gemv_act_norm_residual_norm(float *res, float *y, const float *x, const void *w, const float *nw, float eps, int n, int d, int dtype, int act,
                                      const float *next_w, float *next_out, unsigned *counter, yalm_stream_t s);
 
+/* Decode rows of latent attention on the tensor cores (mma.sync bf16): the heads of a row are the M tile, a tile of 64 cached rows is
+ * fetched once for all heads, for the scores and for the weighted sums.  Sizes: yalm_attn_latent_mma_shape.  nsplit CTAs share a row's
+ * keys (1 ... 64, n n_heads nsplit <= 4096; workspace as for yalm_attn_latent_rows when above 1); the caller picks it from shapes alone.
+ * yalm_attn_latent_merge joins such partials. */
+int yalm_attn_latent_mma_shape(int dk, int dv, int ld);
+int yalm_attn_latent_mma_rows(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *workspace, int n, int n_heads, int dk,
+                              int dv, int ring, int window, float scale, int nsplit, int pos0, const int *ctl, const float *sink, yalm_stream_t s);
+int yalm_attn_latent_merge(float *out, int ldo, const float *part, int n, int n_heads, int dv, int nsplit, const float *sink, yalm_stream_t s);
+
 /* ---- (3a) host-pointer test entry points (src/infer.cu:890-1007 semantics) ------------------- */
 int yalm_matmul_host(float *xout, const float *x, const void *w, const float *scale, int n, int d, int dtype);
 int yalm_mha_host(float *xout, float *att, const uint16_t *kb, const uint16_t *vb, const float *q, int head_dim,

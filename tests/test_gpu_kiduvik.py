@@ -246,6 +246,50 @@ def test_latent_rows_far_key_and_sink(sizes):
     close_enough(got[done], want[done], 2e-3)
 
 
+@pytest.mark.parametrize("H,dk,dv,window,nsplit", [(6, 96, 64, 0, 1), (6, 96, 64, 0, 7), (20, 80, 64, 37, 3), (16, 576, 512, 0, 64), (3, 272, 256, 130, 2), (33, 144, 128, 0, 5)])
+def test_latent_rows_on_the_tensor_cores(H, dk, dv, window, nsplit):
+    """Decode-sized calls with the heads as the M tile: head counts below, at and above 16, key splits from one to more than there are
+    tiles, a window over a wrapping ring, crafted queries at the window's edges, position 0, the far start, and a sink per head."""
+    T, ring = 300, 300 if window == 0 else 192
+    rng = np.random.default_rng(H + dk)
+    rows = O.bf16_round(0.3 * rng.standard_normal((T, dk)))
+    q = O.bf16_round(0.1 * rng.standard_normal((T, H, dk)))
+    size = window if window > 0 else T + 1
+    for t in range(T):
+        for h in range(H):
+            j = [t - size + 1, t - size, 0, t, 3, t - 64][(h + t) % 6]      # oldest inside, newest outside, first, itself, far start, a tile back
+            if 0 <= j <= t:
+                q[t, h] = O.bf16_round(30.0 * rows[j] / (rows[j] @ rows[j]))
+    sink = rng.standard_normal(H) * 3.0
+    want = np.zeros((T, H, dv))
+    for t in range(T):
+        lo = max(0, t - size + 1)
+        for h in range(H):
+            want[t, h] = O.softmax_with_sink(rows[lo:t + 1] @ q[t, h] * 0.5, float(sink[h])) @ rows[lo:t + 1, :dv]
+    R = torch.zeros((ring, dk), dtype=torch.bfloat16, device="cuda")
+    Q, out, ws, sk = dev(q.reshape(T, -1)), torch.zeros((T, H * dv), device="cuda"), workspace(dv), dev(sink)
+    Rall = dev(rows, torch.bfloat16)
+    assert L().yalm_attn_latent_mma_shape(dk, dv, dk) == 1
+    at = 0
+    for n in [1, 1, 3, 2, 1] * 100:
+        n = min(n, T - at)
+        if n <= 0:
+            break
+        for p in range(at, at + n):
+            R[p % ring] = Rall[p]
+        ok(L().yalm_attn_latent_mma_rows(ptr(out[at:]), H * dv, ptr(Q[at:]), H * dk, ptr(R), dk, ptr(ws), n, H, dk, dv, ring, window, f32(0.5), nsplit, at, None, ptr(sk), None),
+           "attn_latent_mma_rows")
+        at += n
+    close_enough(out.cpu().numpy().reshape(T, H, dv), want, 1e-2)     # the weights are bf16 operands of the second product
+    if window > 0:                                                   # the crafted queries make the edge count
+        other = np.zeros((T, H, dv))
+        for t in range(T):
+            lo = max(0, t - size)
+            for h in range(H):
+                other[t, h] = O.softmax_with_sink(rows[lo:t + 1] @ q[t, h] * 0.5, float(sink[h])) @ rows[lo:t + 1, :dv]
+        assert np.abs(other - want).max() > 0.1
+
+
 # ---- small ops -----------------------------------------------------------------------------------------------------------------
 def test_maps_combination():
     rng = np.random.default_rng(7)

@@ -44,6 +44,7 @@ SYMBOLS = [
     "yalm_moe_down_slots_real", "yalm_attn_latent_rows", "yalm_attn_latent_rows_shape", "yalm_add_norm_conv_rows", "yalm_moe_identity_slots", "yalm_latent_gather_rows16", "yalm_latent_pack_rings", "yalm_rotate_heads_rows", "yalm_sigmoid_gate_rows",
     "yalm_attn_window_pool_sink", "yalm_attn_window_pool_mma_sink", "yalm_attn_latent_rows_sink", "yalm_head_norm_rope_append_rows", "yalm_diff_combine_rows",
     "yalm_act_rows", "yalm_token_side_rows", "yalm_token_side_gate_rows", "yalm_gemv_act_norm_residual_norm",
+    "yalm_attn_latent_mma_shape", "yalm_attn_latent_mma_rows", "yalm_attn_latent_merge",
     "yalm_tp_unique_id", "yalm_tp_init", "yalm_tp_finalize", "yalm_tp_shard_plan", "yalm_mega_tile_plan", "yalm_mega_attn_split", "yalm_mega_mma_plan", "yalm_mega_hb_share", "yalm_error_string", "yalm_version",
 ]
 

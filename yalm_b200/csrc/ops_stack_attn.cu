@@ -9,6 +9,7 @@
 // and the weights are fp32, the weights are rounded to bf16 only as the operand of P V.  Per row the mask is an interval
 // of the tile's key indices: blocks [0, nb(i)) or tokens [lo(i), i].
 #include "common.cuh"
+#include "launch.h"
 #include "stack_rows.cuh"
 
 #include <cuda_bf16.h>
@@ -223,6 +224,164 @@ static int launch_mma(float *out, int ldo, const float *q, int ldq, const void *
 	attn_window_pool_mma_kernel<DK, DV><<<dim3((n + 63) / 64, n_heads), 128, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)kr, (const __nv_bfloat16 *)vr,
 	                                                                                   kp, vp, n, n_heads, n_kv, ring, max_blocks, window, pool, scale, pos0,
 	                                                                                   ctl, sink, v_heads);
+	return (int)cudaGetLastError();
+}
+
+
+// ---- decode rows of latent attention on the tensor cores: the heads are the M tile -------------------------------------------
+// Every head of a row reads the same cached rows [latent | rotated key part] (bf16, row stride ld), key = the row's dk channels,
+// value = its first DV.  With the queries already mapped to the cached rows' space (ops_stack_latent.cu: latent_query_rows_kernel),
+// 16 heads x dk is one A operand, a tile of 64 cached rows serves as B for the scores (as stored) and again, transposed by
+// ldmatrix, for the weighted sums, so a cached row is fetched once per CTA for all heads.
+//
+// grid (ceil(heads / 16), rows, key splits), 4 warps.  Tiles of 64 keys go through two shared-memory buffers filled by cp.async.
+// Warp w multiplies the 16 heads by keys 16 w .. 16 w + 15 of the tile over all of dk; the scores (fp32, scaled, masked past the
+// row's position) meet in shared memory; every warp then runs the same online softmax over all 64 and accumulates P V for ITS
+// quarter of the value channels.  One split: the row is finished here (sink included); more: unnormalised partials
+// (accumulator, max, sum) in the layout attn_latent_merge_kernel joins.  Same visibility rule as attn_latent_rows_kernel:
+// position i sees rows j with 0 <= i - j < window (0: all).  Queries and weights are rounded to bf16 as operands; scores, max, sum
+// and accumulators are fp32.
+template <int DV>
+__global__ void __launch_bounds__(128) attn_latent_mma_rows_kernel(float *__restrict__ out, int ldo, const float *__restrict__ q, int ldq,
+                                                                   const __nv_bfloat16 *__restrict__ rows, int ld, float *__restrict__ part, int n_heads,
+                                                                   int dk, int ring, int window, float scale, int pos0, const int *__restrict__ ctl,
+                                                                   const float *__restrict__ sink) {
+	constexpr int DW = DV / 4, OT = DW / 8, LDS = 68; // value channels and 8-wide output tiles per warp; padded score rows
+	extern __shared__ __align__(16) __nv_bfloat16 smb[];
+	const int LDK = dk + 8;                       // padded rows: 16 bytes of skew keep ldmatrix conflict-free
+	__nv_bfloat16 *Qs = smb, *Kbuf = Qs + 16 * LDK;
+	float *Ss = reinterpret_cast<float *>(Kbuf + 2 * 64 * LDK);
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int h0 = blockIdx.x * 16, m = blockIdx.y, z = blockIdx.z, nsplit = gridDim.z;
+	const int i = stack::first_pos(ctl, pos0) + m;
+	const int lo = window > 0 ? max(0, i - window + 1) : 0;
+	const int tiles = (i - lo) / 64 + 1, per = (tiles + nsplit - 1) / nsplit;
+	const int t_begin = z * per, t_end = min(tiles, t_begin + per);
+	// the 16 heads' queries as bf16 (heads past the last: zeros)
+	for (int c = threadIdx.x; c < 16 * (dk / 4); c += 128) {
+		const int r = c / (dk / 4), d = (c % (dk / 4)) * 4;
+		float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+		if (h0 + r < n_heads) v = *reinterpret_cast<const float4 *>(q + (size_t)m * ldq + (size_t)(h0 + r) * dk + d);
+		uint2 pk;
+		pk.x = pack_bf2(v.x, v.y), pk.y = pack_bf2(v.z, v.w);
+		*reinterpret_cast<uint2 *>(Qs + r * LDK + d) = pk;
+	}
+	auto stage = [&](int tt) { // tile tt (positions lo + 64 tt ..) into buffer tt & 1; rows past the position are zero-filled
+		__nv_bfloat16 *Ks = Kbuf + (tt & 1) * 64 * LDK;
+		const int base = lo + tt * 64, pieces = dk / 8;
+		for (int c = threadIdx.x; c < 64 * pieces; c += 128) {
+			const int r = c / pieces, d = (c % pieces) * 8;
+			const bool in = base + r <= i;
+			cp_async16(Ks + r * LDK + d, rows + (size_t)((in ? base + r : i) % ring) * ld + d, in);
+		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+	float o[OT][4];
+#pragma unroll
+	for (int t = 0; t < OT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+	float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f; // heads lane / 4 and lane / 4 + 8 of the 16
+	if (t_begin < t_end) stage(t_begin);
+	for (int tt = t_begin; tt < t_end; ++tt) {
+		const __nv_bfloat16 *Ks = Kbuf + (tt & 1) * 64 * LDK;
+		__syncthreads(); // the previous tile's buffer and scores are read; the queries are in place
+		if (tt + 1 < t_end) {
+			stage(tt + 1);
+			asm volatile("cp.async.wait_group 1;" ::: "memory");
+		} else
+			asm volatile("cp.async.wait_group 0;" ::: "memory");
+		__syncthreads();
+		// ---- scores of this warp's 16 keys ----
+		{
+			float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+			const int ar = (lane & 7) + ((lane >> 3) & 1) * 8, acofs = (lane >> 4) * 8;
+			const int kr = (lane & 7) + (lane >> 4) * 8, kcofs = ((lane >> 3) & 1) * 8;
+			for (int ks = 0; ks < dk / 16; ++ks) {
+				uint32_t a[4], b[4];
+				ldsm_x4(a, (uint32_t)__cvta_generic_to_shared(Qs + ar * LDK + ks * 16 + acofs));
+				ldsm_x4(b, (uint32_t)__cvta_generic_to_shared(Ks + (warp * 16 + kr) * LDK + ks * 16 + kcofs));
+				mma_bf16(s[0], a, b[0], b[1]);
+				mma_bf16(s[1], a, b[2], b[3]);
+			}
+			const int base = lo + tt * 64 + warp * 16;
+#pragma unroll
+			for (int t = 0; t < 2; ++t) {
+				const int col = warp * 16 + t * 8 + (lane & 3) * 2, key = base + t * 8 + (lane & 3) * 2;
+				float *ra = Ss + (lane >> 2) * LDS + col, *rb = Ss + ((lane >> 2) + 8) * LDS + col;
+				ra[0] = key <= i ? s[t][0] * scale : -INFINITY, ra[1] = key + 1 <= i ? s[t][1] * scale : -INFINITY;
+				rb[0] = key <= i ? s[t][2] * scale : -INFINITY, rb[1] = key + 1 <= i ? s[t][3] * scale : -INFINITY;
+			}
+		}
+		__syncthreads();
+		// ---- online softmax over the tile's 64 keys (the same in every warp), then this warp's value channels ----
+		float sa[8][2], sb[8][2], mxA = -INFINITY, mxB = -INFINITY;
+#pragma unroll
+		for (int t = 0; t < 8; ++t) {
+			const float2 va = *reinterpret_cast<const float2 *>(Ss + (lane >> 2) * LDS + t * 8 + (lane & 3) * 2);
+			const float2 vb = *reinterpret_cast<const float2 *>(Ss + ((lane >> 2) + 8) * LDS + t * 8 + (lane & 3) * 2);
+			sa[t][0] = va.x, sa[t][1] = va.y, sb[t][0] = vb.x, sb[t][1] = vb.y;
+			mxA = fmaxf(mxA, fmaxf(va.x, va.y)), mxB = fmaxf(mxB, fmaxf(vb.x, vb.y));
+		}
+		mxA = fmaxf(mxA, __shfl_xor_sync(kFull, mxA, 1)), mxA = fmaxf(mxA, __shfl_xor_sync(kFull, mxA, 2));
+		mxB = fmaxf(mxB, __shfl_xor_sync(kFull, mxB, 1)), mxB = fmaxf(mxB, __shfl_xor_sync(kFull, mxB, 2));
+		const float nA = fmaxf(m0, mxA), nB = fmaxf(m1, mxB); // finite: a tile holds at least one visible key
+		const float cA = m0 == -INFINITY ? 0.f : expf(m0 - nA), cB = m1 == -INFINITY ? 0.f : expf(m1 - nB);
+		m0 = nA, m1 = nB;
+		l0 *= cA, l1 *= cB;
+#pragma unroll
+		for (int t = 0; t < OT; ++t) o[t][0] *= cA, o[t][1] *= cA, o[t][2] *= cB, o[t][3] *= cB;
+		uint32_t pf[4][4]; // the weights as A fragments: key steps of 16
+#pragma unroll
+		for (int t = 0; t < 8; ++t) {
+			const float p0v = expf(sa[t][0] - nA), p1v = expf(sa[t][1] - nA), p2v = expf(sb[t][0] - nB), p3v = expf(sb[t][1] - nB);
+			l0 += p0v + p1v, l1 += p2v + p3v;
+			pf[t >> 1][(t & 1) * 2] = pack_bf2(p0v, p1v);
+			pf[t >> 1][(t & 1) * 2 + 1] = pack_bf2(p2v, p3v);
+		}
+		{
+			const int vr = (lane & 7) + ((lane >> 3) & 1) * 8, vcofs = (lane >> 4) * 8;
+#pragma unroll
+			for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+				for (int t = 0; t < OT; t += 2) {
+					uint32_t b[4];
+					ldsm_x4_t(b, (uint32_t)__cvta_generic_to_shared(Ks + (kk * 16 + vr) * LDK + warp * DW + t * 8 + vcofs));
+					mma_bf16(o[t], pf[kk], b[0], b[1]);
+					mma_bf16(o[t + 1], pf[kk], b[2], b[3]);
+				}
+		}
+	}
+	l0 += __shfl_xor_sync(kFull, l0, 1), l0 += __shfl_xor_sync(kFull, l0, 2);
+	l1 += __shfl_xor_sync(kFull, l1, 1), l1 += __shfl_xor_sync(kFull, l1, 2);
+	const int hA = h0 + (lane >> 2), hB = hA + 8;
+	if (part) {
+		float *pa = part + ((size_t)(m * n_heads + hA) * nsplit + z) * (DV + 2), *pb = part + ((size_t)(m * n_heads + hB) * nsplit + z) * (DV + 2);
+#pragma unroll
+		for (int t = 0; t < OT; ++t) {
+			const int d = warp * DW + t * 8 + (lane & 3) * 2;
+			if (hA < n_heads) pa[d] = o[t][0], pa[d + 1] = o[t][1];
+			if (hB < n_heads) pb[d] = o[t][2], pb[d + 1] = o[t][3];
+		}
+		if (warp == 0 && (lane & 3) == 0) {
+			if (hA < n_heads) pa[DV] = m0, pa[DV + 1] = l0;
+			if (hB < n_heads) pb[DV] = m1, pb[DV + 1] = l1;
+		}
+	} else {
+		const float f0 = hA < n_heads ? stack::softmax_finish(m0, l0, sink, hA) : 0.f, f1 = hB < n_heads ? stack::softmax_finish(m1, l1, sink, hB) : 0.f;
+#pragma unroll
+		for (int t = 0; t < OT; ++t) {
+			const int d = warp * DW + t * 8 + (lane & 3) * 2;
+			if (hA < n_heads) out[(size_t)m * ldo + (size_t)hA * DV + d] = o[t][0] * f0, out[(size_t)m * ldo + (size_t)hA * DV + d + 1] = o[t][1] * f0;
+			if (hB < n_heads) out[(size_t)m * ldo + (size_t)hB * DV + d] = o[t][2] * f1, out[(size_t)m * ldo + (size_t)hB * DV + d + 1] = o[t][3] * f1;
+		}
+	}
+}
+
+template <int DV>
+static int launch_latent_mma(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *part, int n, int n_heads, int dk, int ring,
+                             int window, float scale, int nsplit, int pos0, const int *ctl, const float *sink, size_t smem, cudaStream_t st) {
+	if (smem > 48 * 1024) YALM_TRY(cudaFuncSetAttribute(attn_latent_mma_rows_kernel<DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	attn_latent_mma_rows_kernel<DV><<<dim3((n_heads + 15) / 16, n, nsplit), 128, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)rows, ld, part, n_heads, dk,
+	                                                                                       ring, window, scale, pos0, ctl, sink);
 	return (int)cudaGetLastError();
 }
 
@@ -455,6 +614,34 @@ extern "C" int yalm_attn_window_pool_mma_sink(float *out, int ldo, const float *
 	MMA_CASE(128, 128);
 #undef MMA_CASE
 	return YALM_EINVAL;
+}
+
+// 1 when yalm_attn_latent_mma_rows has a kernel for these sizes: key size a multiple of 16 whose two tile buffers fit into shared
+// memory, value size 64, 128, 256 or 512 (at most the key size), row stride a multiple of 8.
+static size_t latent_mma_smem(int dk) { return sizeof(__nv_bfloat16) * (size_t)(16 + 2 * 64) * (dk + 8) + sizeof(float) * 16 * 68; }
+extern "C" int yalm_attn_latent_mma_shape(int dk, int dv, int ld) {
+	return dk >= 16 && dk % 16 == 0 && (dv == 64 || dv == 128 || dv == 256 || dv == 512) && dv <= dk && ld >= dk && ld % 8 == 0 &&
+	       (int)latent_mma_smem(dk) <= yalm::device_info().max_smem_optin;
+}
+
+// The tensor-core route of yalm_attn_latent_rows_sink for decode-sized calls: q (n, n_heads dk) fp32 already in the cached rows'
+// space, rows bf16 (16-byte aligned).  nsplit: how many CTAs share a row's keys (1 ... 64; workspace as for yalm_attn_latent_rows
+// when above 1), chosen by the caller from shapes alone.
+extern "C" int yalm_attn_latent_mma_rows(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *workspace, int n, int n_heads, int dk,
+                                         int dv, int ring, int window, float scale, int nsplit, int pos0, const int *ctl, const float *sink, yalm_stream_t s) {
+	if (!out || !q || !rows || n < 1 || n_heads < 1 || ring < 1 || nsplit < 1 || nsplit > 64 || (nsplit > 1 && !workspace) || !yalm_attn_latent_mma_shape(dk, dv, ld) ||
+	    ((uintptr_t)rows & 15) || ((uintptr_t)q & 15) || ldq % 4 || (long)n * n_heads * nsplit > 4096)
+		return YALM_EINVAL;
+	cudaStream_t st = (cudaStream_t)s;
+	const size_t smem = latent_mma_smem(dk);
+	float *part = nsplit > 1 ? workspace : nullptr;
+	int rc;
+	if (dv == 64) rc = launch_latent_mma<64>(out, ldo, q, ldq, rows, ld, part, n, n_heads, dk, ring, window, scale, nsplit, pos0, ctl, sink, smem, st);
+	else if (dv == 128) rc = launch_latent_mma<128>(out, ldo, q, ldq, rows, ld, part, n, n_heads, dk, ring, window, scale, nsplit, pos0, ctl, sink, smem, st);
+	else if (dv == 256) rc = launch_latent_mma<256>(out, ldo, q, ldq, rows, ld, part, n, n_heads, dk, ring, window, scale, nsplit, pos0, ctl, sink, smem, st);
+	else rc = launch_latent_mma<512>(out, ldo, q, ldq, rows, ld, part, n, n_heads, dk, ring, window, scale, nsplit, pos0, ctl, sink, smem, st);
+	if (rc || nsplit == 1) return rc;
+	return yalm_attn_latent_merge(out, ldo, workspace, n, n_heads, dv, nsplit, sink, s);
 }
 
 // 1 when yalm_attn_sigmoid_mma has a kernel for this head size (bf16 ring only).

@@ -778,3 +778,10 @@ extern "C" int yalm_attn_latent_rows_sink(float *out, int ldo, const float *q, i
 #undef LA_CASE
 	return YALM_EINVAL;
 }
+
+// Joins nsplit (<= 64) partials per (row, head) of (dv accumulators, max, sum) in `part`, in order, sink included (null: none).
+extern "C" int yalm_attn_latent_merge(float *out, int ldo, const float *part, int n, int n_heads, int dv, int nsplit, const float *sink, yalm_stream_t s) {
+	if (!out || !part || n < 1 || n_heads < 1 || dv < 1 || nsplit < 1 || nsplit > 64) return YALM_EINVAL;
+	attn_latent_merge_kernel<<<dim3(n_heads, n), 128, 0, (cudaStream_t)s>>>(out, ldo, part, n_heads, dv, nsplit, sink);
+	return (int)cudaGetLastError();
+}
