@@ -567,9 +567,10 @@ __global__ void attn_latent_merge_kernel(float *__restrict__ out, int ldo, const
 			if (lane + 32 * k < nsplit) wz[lane + 32 * k] = e[k] * fin;
 	}
 	__syncthreads();
-	for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+	// grid.z cuts the channels: a thread's loads over the splits are independent, and more CTAs keep more of them in flight
+	for (int c = blockIdx.z * blockDim.x + threadIdx.x; c < dv; c += gridDim.z * blockDim.x) {
 		float o = 0.f;
-#pragma unroll 8
+#pragma unroll 16
 		for (int z = 0; z < nsplit; ++z) o = fmaf(wz[z], pr[(size_t)z * (dv + 2) + c], o);
 		out[(size_t)m * ldo + (size_t)h * dv + c] = o;
 	}
@@ -747,7 +748,7 @@ static int launch_attn_latent(float *out, int ldo, const float *q, int ldq, cons
 	attn_latent_rows_kernel<R, NP><<<dim3((n_heads + R - 1) / R, n, nsplit), kLaWarps * 32, smem, st>>>(out, ldo, q, ldq, (const __nv_bfloat16 *)rows, ld,
 	                                                                                                  nsplit > 1 ? ws : nullptr, n_heads, dk, dv, ring,
 	                                                                                                  window, scale, pos0, ctl, sink);
-	if (nsplit > 1) attn_latent_merge_kernel<<<dim3(n_heads, n), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit, sink);
+	if (nsplit > 1) attn_latent_merge_kernel<<<dim3(n_heads, n, (dv + 127) / 128), 128, 0, st>>>(out, ldo, ws, n_heads, dv, nsplit, sink);
 	return (int)cudaGetLastError();
 }
 
@@ -782,6 +783,6 @@ extern "C" int yalm_attn_latent_rows_sink(float *out, int ldo, const float *q, i
 // Joins nsplit (<= 64) partials per (row, head) of (dv accumulators, max, sum) in `part`, in order, sink included (null: none).
 extern "C" int yalm_attn_latent_merge(float *out, int ldo, const float *part, int n, int n_heads, int dv, int nsplit, const float *sink, yalm_stream_t s) {
 	if (!out || !part || n < 1 || n_heads < 1 || dv < 1 || nsplit < 1 || nsplit > 64) return YALM_EINVAL;
-	attn_latent_merge_kernel<<<dim3(n_heads, n), 128, 0, (cudaStream_t)s>>>(out, ldo, part, n_heads, dv, nsplit, sink);
+	attn_latent_merge_kernel<<<dim3(n_heads, n, (dv + 127) / 128), 128, 0, (cudaStream_t)s>>>(out, ldo, part, n_heads, dv, nsplit, sink);
 	return (int)cudaGetLastError();
 }
