@@ -427,7 +427,7 @@ int yalm_gemv_act_norm_residual_norm(float *res, float *y, const float *x, const
 
 /* Decode rows of latent attention on the tensor cores (mma.sync bf16): the heads of a row are the M tile, a tile of 64 cached rows is
  * fetched once for all heads, for the scores and for the weighted sums.  Sizes: yalm_attn_latent_mma_shape.  nsplit CTAs share a row's
- * keys (1 ... 64, n n_heads nsplit <= 4096; workspace as for yalm_attn_latent_rows when above 1); the caller picks it from shapes alone.
+ * keys (1 ... 128, n n_heads nsplit <= 4096; workspace as for yalm_attn_latent_rows when above 1); the caller picks it from shapes alone.
  * yalm_attn_latent_merge joins such partials. */
 int yalm_attn_latent_mma_shape(int dk, int dv, int ld);
 int yalm_attn_latent_mma_rows(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *workspace, int n, int n_heads, int dk,

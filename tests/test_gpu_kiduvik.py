@@ -246,7 +246,7 @@ def test_latent_rows_far_key_and_sink(sizes):
     close_enough(got[done], want[done], 2e-3)
 
 
-@pytest.mark.parametrize("H,dk,dv,window,nsplit", [(6, 96, 64, 0, 1), (6, 96, 64, 0, 7), (20, 80, 64, 37, 3), (16, 576, 512, 0, 64), (3, 272, 256, 130, 2), (33, 144, 128, 0, 5)])
+@pytest.mark.parametrize("H,dk,dv,window,nsplit", [(6, 96, 64, 0, 1), (6, 96, 64, 0, 7), (20, 80, 64, 37, 3), (16, 576, 512, 0, 64), (7, 96, 64, 0, 128), (3, 272, 256, 130, 2), (33, 144, 128, 0, 5)])
 def test_latent_rows_on_the_tensor_cores(H, dk, dv, window, nsplit):
     """Decode-sized calls with the heads as the M tile: head counts below, at and above 16, key splits from one to more than there are
     tiles, a window over a wrapping ring, crafted queries at the window's edges, position 0, the far start, and a sink per head."""

@@ -625,11 +625,11 @@ extern "C" int yalm_attn_latent_mma_shape(int dk, int dv, int ld) {
 }
 
 // The tensor-core route of yalm_attn_latent_rows_sink for decode-sized calls: q (n, n_heads dk) fp32 already in the cached rows'
-// space, rows bf16 (16-byte aligned).  nsplit: how many CTAs share a row's keys (1 ... 64; workspace as for yalm_attn_latent_rows
+// space, rows bf16 (16-byte aligned).  nsplit: how many CTAs share a row's keys (1 ... 128; workspace as for yalm_attn_latent_rows
 // when above 1), chosen by the caller from shapes alone.
 extern "C" int yalm_attn_latent_mma_rows(float *out, int ldo, const float *q, int ldq, const void *rows, int ld, float *workspace, int n, int n_heads, int dk,
                                          int dv, int ring, int window, float scale, int nsplit, int pos0, const int *ctl, const float *sink, yalm_stream_t s) {
-	if (!out || !q || !rows || n < 1 || n_heads < 1 || ring < 1 || nsplit < 1 || nsplit > 64 || (nsplit > 1 && !workspace) || !yalm_attn_latent_mma_shape(dk, dv, ld) ||
+	if (!out || !q || !rows || n < 1 || n_heads < 1 || ring < 1 || nsplit < 1 || nsplit > 128 || (nsplit > 1 && !workspace) || !yalm_attn_latent_mma_shape(dk, dv, ld) ||
 	    ((uintptr_t)rows & 15) || ((uintptr_t)q & 15) || ldq % 4 || (long)n * n_heads * nsplit > 4096)
 		return YALM_EINVAL;
 	cudaStream_t st = (cudaStream_t)s;

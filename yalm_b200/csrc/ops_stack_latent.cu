@@ -542,28 +542,28 @@ __global__ void __launch_bounds__(kLaWarps * 32) attn_latent_rows_kernel(float *
 // M = -inf and no weight).  grid (heads, rows).
 __global__ void attn_latent_merge_kernel(float *__restrict__ out, int ldo, const float *__restrict__ part, int n_heads, int dv, int nsplit,
                                          const float *__restrict__ sink) {
-	__shared__ float wz[64]; // the splits' weights over the common sum (nsplit <= 64)
+	__shared__ float wz[128]; // the splits' weights over the common sum (nsplit <= 128)
 	const int h = blockIdx.x, m = blockIdx.y;
 	const float *pr = part + (size_t)(m * n_heads + h) * nsplit * (dv + 2);
-	if (threadIdx.x < 32) { // lane = split
+	if (threadIdx.x < 32) { // lane = split (and split + 32, + 64, + 96)
 		const int lane = threadIdx.x;
-		float mz[2], lz[2];
+		float mz[4], lz[4];
 #pragma unroll
-		for (int k = 0; k < 2; ++k) {
+		for (int k = 0; k < 4; ++k) {
 			const int z = lane + 32 * k;
 			mz[k] = z < nsplit ? pr[(size_t)z * (dv + 2) + dv] : -INFINITY;
 			lz[k] = z < nsplit ? pr[(size_t)z * (dv + 2) + dv + 1] : 0.f;
 		}
-		const float M = warp_max(fmaxf(mz[0], mz[1]));
-		float e[2];
+		const float M = warp_max(fmaxf(fmaxf(mz[0], mz[1]), fmaxf(mz[2], mz[3])));
+		float e[4], t[4];
 #pragma unroll
-		for (int k = 0; k < 2; ++k) e[k] = mz[k] == -INFINITY ? 0.f : expf(mz[k] - M);
+		for (int k = 0; k < 4; ++k) e[k] = mz[k] == -INFINITY ? 0.f : expf(mz[k] - M), t[k] = e[k] * lz[k];
 		// the sum runs over the splits in order
 		float L = 0.f;
-		for (int z = 0; z < nsplit; ++z) L += __shfl_sync(kFull, z < 32 ? e[0] * lz[0] : e[1] * lz[1], z & 31);
+		for (int z = 0; z < nsplit; ++z) L += __shfl_sync(kFull, z < 32 ? t[0] : z < 64 ? t[1] : z < 96 ? t[2] : t[3], z & 31);
 		const float fin = softmax_finish(M, L, sink, h);
 #pragma unroll
-		for (int k = 0; k < 2; ++k)
+		for (int k = 0; k < 4; ++k)
 			if (lane + 32 * k < nsplit) wz[lane + 32 * k] = e[k] * fin;
 	}
 	__syncthreads();
@@ -780,9 +780,9 @@ extern "C" int yalm_attn_latent_rows_sink(float *out, int ldo, const float *q, i
 	return YALM_EINVAL;
 }
 
-// Joins nsplit (<= 64) partials per (row, head) of (dv accumulators, max, sum) in `part`, in order, sink included (null: none).
+// Joins nsplit (<= 128) partials per (row, head) of (dv accumulators, max, sum) in `part`, in order, sink included (null: none).
 extern "C" int yalm_attn_latent_merge(float *out, int ldo, const float *part, int n, int n_heads, int dv, int nsplit, const float *sink, yalm_stream_t s) {
-	if (!out || !part || n < 1 || n_heads < 1 || dv < 1 || nsplit < 1 || nsplit > 64) return YALM_EINVAL;
+	if (!out || !part || n < 1 || n_heads < 1 || dv < 1 || nsplit < 1 || nsplit > 128) return YALM_EINVAL;
 	attn_latent_merge_kernel<<<dim3(n_heads, n, (dv + 127) / 128), 128, 0, (cudaStream_t)s>>>(out, ldo, part, n_heads, dv, nsplit, sink);
 	return (int)cudaGetLastError();
 }

@@ -1155,9 +1155,9 @@ int Model::stack_layer_sandwich(StackScratch &S, const yalm::StackLayer &L, cons
 			                              a.rot.interleaved ? 1 : 0, pos0, ctl, st));
 			static const bool latent_mma_off = [] { const char *e = getenv("YALM_STACK_LATENT_MMA"); return e && e[0] == '0'; }(); // A/B against the SIMT kernel
 			if (!f32 && !latent_mma_off && yalm_attn_latent_mma_shape(row, a.kv_rank, row) && ((uintptr_t)L.kring & 15) == 0 && nqa % 4 == 0 && n * m.heads <= 4096) {
-				// the heads as the M tile of the tensor cores; the keys a row can ever see, in tiles of 64, are split over up to 64 CTAs (shapes only)
+				// the heads as the M tile of the tensor cores; the keys a row can ever see, in tiles of 64, are split over up to 128 CTAs (shapes only)
 				const int tiles = ((m.window > 0 ? std::min(m.window, c.max_seq_len) : c.max_seq_len) + 63) / 64, ctas = (m.heads + 15) / 16 * n;
-				const int cap = std::max(1, std::min({tiles, 64, 4096 / (n * m.heads), (296 + ctas - 1) / ctas}));
+				const int cap = std::max(1, std::min({tiles, 128, 4096 / (n * m.heads), (296 + ctas - 1) / ctas}));
 				const int per = (tiles + cap - 1) / cap, nsplit = (tiles + per - 1) / per;
 				ST_TRY(yalm_attn_latent_mma_rows(S.scan, nl, S.aux, nqa, L.kring, row, S.attn_ws, n, m.heads, row, a.kv_rank, L.ring, m.window, m.scale, nsplit, pos0,
 				                                 ctl, L.sink, st));
