@@ -623,7 +623,7 @@ def test_trace_runner(tmp_path):
     cfg = five_layers()
     folder, W = checkpoint(tmp_path, cfg, seed=14)
     a, b = tokens_for(cfg, 25, 4), tokens_for(cfg, 9, 5)
-    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:20], "want": [3, 19]}], "end": []},
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:20], "want": [19, 3, 19]}], "end": []},   # rows come in the order asked
              {"step": 1, "entries": [{"id": "a", "tokens": a[20:22], "want": []}], "end": []},
              {"step": 2, "entries": [{"id": "a", "tokens": a[22:], "want": [2]}], "end": ["a"]},
              {"step": 3, "entries": [{"id": "b", "tokens": b, "want": [8]}], "end": ["b"]}]
@@ -637,7 +637,7 @@ def test_trace_runner(tmp_path):
         assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == ["done 0", "done 1", "done 2", "done 3"]
         wa, wb = O.forward(cfg, W, a)[0], O.forward(cfg, W, b)[0]
         V = cfg["vocab"]
-        close_enough(np.fromfile(out / "0.f32", "<f4").reshape(-1, V), wa[[3, 19]], tol)
+        close_enough(np.fromfile(out / "0.f32", "<f4").reshape(-1, V), wa[[19, 3, 19]], tol)
         assert not (out / "1.f32").exists()
         close_enough(np.fromfile(out / "2.f32", "<f4").reshape(-1, V), wa[[24]], tol)
         close_enough(np.fromfile(out / "3.f32", "<f4").reshape(-1, V), wb[[8]], tol)
