@@ -440,8 +440,8 @@ def write_kiduvik(folder, z, context):
     mlp = {"kind": "dense", "ff": z["ff"]}
     lat = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"], "rot": {"base": 10000.0, "dims": z["rot"]},
            "scale": (z["dim"] + z["rot"]) ** -0.5}
-    dif = {"heads": z["dheads"], "kv_heads": z["dkv"], "dim": z["ddim"], "vdim": z["dvdim"], "diff": 0.6, "mask": {"size": z["window"], "keep_first": z["keep"]},
-           "rot": {"base": 250000.0, "dims": z["ddim"] // 2, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}, "scale": z["ddim"] ** -0.5}
+    dif = {"heads": z["dheads"], "kv_heads": z["dkv"], "dim": z["ddim"], "vdim": z["dvdim"], "diff": 0.8, "mask": {"size": z["window"], "keep_first": z["keep"]},
+           "rot": {"base": 500000.0, "dims": z["ddim"] // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}, "scale": z["ddim"] ** -0.5}
     layers = [{"type": "latent_attention", "mixer": lat, "mlp": mlp} if c == "l" else
               {"type": "latent_attention", "mixer": dict(lat, kv_from=z["order"].index("l")), "mlp": mlp} if c == "s" else
               {"type": "attention", "mixer": dif, "mlp": mlp} for c in z["order"]]
